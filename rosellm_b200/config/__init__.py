@@ -14,6 +14,7 @@ from .engine import EngineConfig
 from .gpt2 import GPT2Config
 from .lebedra import LebedraConfig
 from .porovik import PorovikConfig
+from .fikevik import FikevikConfig
 
 __all__ = [
     "Architecture",

@@ -5,6 +5,9 @@
 //   score(i, j) = (q_i . k_j) * scale * temp(i) - slope_h * (i - j),  j <= i
 //   temp(i)     = 1 + temp_coef * ln(floor((i + 1) / temp_every) + 1)          (temp_every = 0: 1)
 //   slope_h     : a table the caller gives, one entry a head                    (absent: no bias)
+//   head_scale  : a further factor of the score per head, from a table            (absent: 1)
+//   window      : a query at i sees the keys j with 0 <= i - j < window            (0: all keys j <= i);
+//                 pages that lie wholly before a block's window are never looked up (the cache gives them back)
 //   out         = softmax(score) V * sigmoid(gate)                             (gate absent: no gate)
 //
 // Scores, softmax and the weighted sums are float32 whatever the cache holds.  Queries and gate logits are
@@ -43,6 +46,8 @@ struct BiasAttnParams {
   int temp_every;
   const float* slopes;  // [n_heads] or null
   int* status;
+  int window;               // 0: none
+  const float* head_scale;  // [n_heads] or null
   // decoded tokens whose keys are cut into parts: a block takes one part and leaves its unnormalised sums
   // in part_o [(decoded request, head, part), dv] and (maximum, sum of weights) in part_ml
   int n_splits;
@@ -114,6 +119,7 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
     float temp = 1.0f;
     if (p.temp_every > 0) temp = 1.0f + p.temp_coef * logf((float)((row_pos[a] + 1) / p.temp_every + 1));
     row_mul[a] = p.scale * temp;
+    if (p.head_scale != nullptr && row_ok[a]) row_mul[a] *= p.head_scale[row_head[a]];
     row_slope[a] = (p.slopes != nullptr && row_ok[a]) ? p.slopes[row_head[a]] : 0.f;
     m[a] = -CUDART_INF_F;
     l[a] = 0.f;
@@ -121,6 +127,7 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
     for (int c = 0; c < DVC; ++c) acc[a][c] = 0.f;
   }
   const int last_pos = pos0 + n_tok - 1;
+  const int first_seen = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;  // the earliest key any row of the block sees
   const T* pool = reinterpret_cast<const T*>(p.pool);
   const int* table = p.block_table + (size_t)slot * p.ldt;
   // Where each key of a tile lies (null: beyond the block's last position, or no page): looked up by one
@@ -131,7 +138,7 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
     if (tid < BA_KEYS) {
       const int j = j0 + tid;
       const T* src = nullptr;
-      if (j <= last_pos) {
+      if (j <= last_pos && j >= first_seen) {
         const int lp = j / p.page_size;
         const int page = lp < p.max_pages ? table[lp] : -1;
         if (page < 0)
@@ -146,12 +153,12 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
   const bool vec = dk % EV == 0 && dv % EV == 0 && p.row % EV == 0 && p.v_at % EV == 0 &&
                    (reinterpret_cast<uintptr_t>(p.pool) & 15) == 0;
   for (int i = tid; i < BA_KEYS * ldv_s; i += BA_THREADS) Vs[i] = 0.f;  // the fill beyond dv stays zero
-  int j_begin = 0, j_end = last_pos + 1;  // the keys this block walks
+  int j_begin = first_seen / BA_KEYS * BA_KEYS, j_end = last_pos + 1;  // the keys this block walks
   if (parted) {
-    const int tiles_all = (last_pos + BA_KEYS) / BA_KEYS;
+    const int tiles_all = (last_pos + BA_KEYS) / BA_KEYS - j_begin / BA_KEYS;
     const int per = (tiles_all + p.n_splits - 1) / p.n_splits;
-    j_begin = split * per * BA_KEYS;
-    j_end = min(j_end, (split + 1) * per * BA_KEYS);
+    j_end = min(j_end, j_begin + (split + 1) * per * BA_KEYS);
+    j_begin += split * per * BA_KEYS;
   }
   locate(j_begin, 0);
   int buf = 0;
@@ -207,7 +214,7 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
 #pragma unroll
       for (int b = 0; b < KPT; ++b) {
         const int j = j0 + tx + LPR * b;
-        const bool see = row_ok[a] && j <= row_pos[a];
+        const bool see = row_ok[a] && j <= row_pos[a] && (p.window <= 0 || row_pos[a] - j < p.window);
         s[a][b] = see ? s[a][b] * row_mul[a] - row_slope[a] * (float)(row_pos[a] - j) : -CUDART_INF_F;
         tile_max = fmaxf(tile_max, s[a][b]);
       }
@@ -421,10 +428,11 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
                                 const int* decode_reqs, int n_decode, void* out, long ldo, int n_heads, int n_kv, int dk,
                                 int dv, int v_at, int row, int page_size, int max_pages, float scale, float temp_coef,
                                 int temp_every, const float* slopes, int* status, int n_splits, float* part_o,
-                                float* part_ml, int tensor_cores, cudaStream_t stream) {
+                                float* part_ml, int tensor_cores, int window, const float* head_scale,
+                                cudaStream_t stream) {
   if (n_tiles <= 0 && n_decode <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || v_at < dk ||
-      v_at + dv > row || n_kv > 65535)
+      v_at + dv > row || n_kv > 65535 || window < 0)
     return -2;
   // prompt tiles on the tensor cores: bfloat16 cache and output, per-head sizes up to 128
   const bool mma = tensor_cores && cache_dtype == RL_BF16 && out_dtype == RL_BF16 && dk <= 128 && dv <= 128;
@@ -437,7 +445,7 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
   const int hg = n_heads / n_kv;
   rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
                        n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
-                       tt, hb, 0, scale, temp_coef, temp_every, slopes, status, 1, part_o, part_ml};
+                       tt, hb, 0, scale, temp_coef, temp_every, slopes, status, window, head_scale, 1, part_o, part_ml};
   if (p.n_tiles > 0) {  // the prompt portions: 32 or 64 rows a block, cut into tokens and heads as rl_bias_attention_shape says
     const dim3 grid(p.n_tiles * (tile_tokens / tt), n_kv, (hg + hb - 1) / hb);
     if (mma) rl::dispatch_bias_attn_mma(p, grid, stream);
@@ -480,6 +488,85 @@ RL_EXPORT int rl_bias_kv_store(int cache_dtype, const float* k, long ldk, const 
     rl::launch_pdl(rl::bias_kv_store_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, k, ldk, v, ldv, v_src, lambda,
                    mix, (__nv_bfloat16*)pool, block_table, ldt, positions, req_of_token, slots, n_tokens, n_kv, dk, dv,
                    v_at, row, page_size, max_pages, status);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+namespace rl {
+
+// What a layer does to its queries, keys and values between the projections and the cache, in place on the
+// float32 columns of the packed projections, a warp a (token, head):
+//   queries and keys: each head's entries divided by their root mean square (eps inside the root) and
+//     multiplied by a weight the heads share (q_norm / k_norm; absent: left as they are), then the first
+//     `rot_dims` entries turned, entry 2i with entry 2i + 1, by the angle position * freq[i];
+//   values: each head's entries divided by their root mean square, no weight (unit_values; else untouched).
+// Angles are formed and evaluated in float32.
+__global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict__ q, long ldq, float* __restrict__ k,
+                                                              long ldk, float* __restrict__ v, long ldv,
+                                                              const float* __restrict__ q_norm,
+                                                              const float* __restrict__ k_norm,
+                                                              const float* __restrict__ freq,
+                                                              const int* __restrict__ positions, int n_tokens,
+                                                              int n_heads, int n_kv, int dk, int dv, int rot_dims,
+                                                              int unit_values, float eps) {
+  pdl_begin();
+  const int tok = blockIdx.x;
+  if (tok >= n_tokens) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const float pos = (float)positions[tok];
+  const int units = n_heads + n_kv + (unit_values ? n_kv : 0);
+  for (int u = warp; u < units; u += n_warps) {
+    if (u < n_heads + n_kv) {
+      const bool is_q = u < n_heads;
+      float* e = is_q ? q + (size_t)tok * ldq + (size_t)u * dk : k + (size_t)tok * ldk + (size_t)(u - n_heads) * dk;
+      const float* w = is_q ? q_norm : k_norm;
+      float r = 1.0f;
+      if (w != nullptr) {
+        float ss = 0.f;
+        for (int d = lane; d < dk; d += 32) ss = fmaf(e[d], e[d], ss);
+        r = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+      }
+      for (int i = lane; 2 * i < dk; i += 32) {  // a lane takes whole pairs; an odd last entry has no partner
+        const int d0 = 2 * i, d1 = 2 * i + 1;
+        float a = e[d0] * r, b = d1 < dk ? e[d1] * r : 0.f;
+        if (w != nullptr) {
+          a *= w[d0];
+          if (d1 < dk) b *= w[d1];
+        }
+        if (d1 < rot_dims) {
+          float sn, cs;
+          sincosf(pos * freq[i], &sn, &cs);
+          const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+          a = ra;
+          b = rb;
+        }
+        e[d0] = a;
+        if (d1 < dk) e[d1] = b;
+      }
+    } else {
+      float* e = v + (size_t)tok * ldv + (size_t)(u - n_heads - n_kv) * dv;
+      float ss = 0.f;
+      for (int d = lane; d < dv; d += 32) ss = fmaf(e[d], e[d], ss);
+      const float r = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+      for (int d = lane; d < dv; d += 32) e[d] *= r;
+    }
+  }
+}
+
+}  // namespace rl
+
+// Queries [tokens, heads * dk], keys [tokens, kv heads * dk] and values [tokens, kv heads * dv] (float32, row
+// strides given) normalised and rotated in place; see the kernel.  q_norm / k_norm: float32 [dk] or null (both
+// or neither); freq: float32 [rot_dims / 2] (rot_dims even, at most dk; 0: no rotation).
+RL_EXPORT int rl_qkv_norm_rotate(float* q, long ldq, float* k, long ldk, float* v, long ldv, const float* q_norm,
+                                 const float* k_norm, const float* freq, const int* positions, int n_tokens, int n_heads,
+                                 int n_kv, int dk, int dv, int rot_dims, int unit_values, float eps, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (n_heads <= 0 || n_kv <= 0 || dk <= 0 || dv <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > dk ||
+      (rot_dims > 0 && freq == nullptr) || (q_norm == nullptr) != (k_norm == nullptr))
+    return -2;
+  rl::launch_pdl(rl::qkv_norm_rotate_kernel, n_tokens, 128, 0, stream, q, ldq, k, ldk, v, ldv, q_norm, k_norm, freq,
+                 positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, eps);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -77,6 +77,7 @@ __global__ __launch_bounds__(BM_THREADS) void bias_attn_mma_kernel(const BiasAtt
     float temp = 1.0f;
     if (p.temp_every > 0) temp = 1.0f + p.temp_coef * logf((float)((row_pos[a] + 1) / p.temp_every + 1));
     row_mul[a] = p.scale * temp;
+    if (p.head_scale != nullptr && row_ok[a]) row_mul[a] *= p.head_scale[row_head[a]];
     row_slope[a] = (p.slopes != nullptr && row_ok[a]) ? p.slopes[row_head[a]] : 0.f;
     m[a] = -CUDART_INF_F;
     l[a] = 0.f;
@@ -85,13 +86,14 @@ __global__ __launch_bounds__(BM_THREADS) void bias_attn_mma_kernel(const BiasAtt
 #pragma unroll
   for (int nt = 0; nt < DVT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
   const int last_pos = pos0 + n_tok - 1;
+  const int first_seen = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;  // the earliest key any row of the block sees
   const __nv_bfloat16* pool = reinterpret_cast<const __nv_bfloat16*>(p.pool);
   const int* table = p.block_table + (size_t)slot * p.ldt;
   auto locate = [&](int j0, int buf) {
     if (tid < BM_KEYS) {
       const int j = j0 + tid;
       const __nv_bfloat16* src = nullptr;
-      if (j <= last_pos) {
+      if (j <= last_pos && j >= first_seen) {
         const int lp = j / p.page_size;
         const int page = lp < p.max_pages ? table[lp] : -1;
         if (page < 0)
@@ -103,12 +105,13 @@ __global__ __launch_bounds__(BM_THREADS) void bias_attn_mma_kernel(const BiasAtt
     }
   };
   const bool vec = dk % 8 == 0 && dv % 8 == 0 && (reinterpret_cast<uintptr_t>(p.pool) & 15) == 0;
-  locate(0, 0);
+  const int j_begin = first_seen / BM_KEYS * BM_KEYS;
+  locate(j_begin, 0);
   int buf = 0;
   const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qs);
   const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Ks);
   const uint32_t* Vw = reinterpret_cast<const uint32_t*>(Vt);
-  for (int j0 = 0; j0 <= last_pos; j0 += BM_KEYS, buf ^= 1) {
+  for (int j0 = j_begin; j0 <= last_pos; j0 += BM_KEYS, buf ^= 1) {
     __syncthreads();  // the tile before has been used; this tile's places (and, the first time, the queries) are known
     if (vec) {
       const int kp = dk / 8, vp = dv / 8, per_key = kp + vp;
@@ -172,7 +175,7 @@ __global__ __launch_bounds__(BM_THREADS) void bias_attn_mma_kernel(const BiasAtt
         for (int e = 0; e < 2; ++e) {
           const int j = j0 + nt * 8 + 2 * in_quad + e;
           float& v = s[nt][2 * a + e];
-          const bool see = row_ok[a] && j <= row_pos[a];
+          const bool see = row_ok[a] && j <= row_pos[a] && (p.window <= 0 || row_pos[a] - j < p.window);
           v = see ? v * row_mul[a] - row_slope[a] * (float)(row_pos[a] - j) : -CUDART_INF_F;
           tile_max = fmaxf(tile_max, v);
         }

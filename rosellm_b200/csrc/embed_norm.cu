@@ -14,7 +14,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
                              const T* __restrict__ table, const T* __restrict__ pos_table,
                              float* __restrict__ out, int n_tokens, int hidden, int vocab,
                              int n_positions, int* __restrict__ status,
-                             const int* __restrict__ feedback, int n_feedback) {
+                             const int* __restrict__ feedback, int n_feedback, float scale) {
   pdl_begin();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
@@ -40,7 +40,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     p = pos_table + (size_t)ps * hidden;
   }
   for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
-    float v = to_f32(e[d]);
+    float v = to_f32(e[d]) * scale;  // the token's row times the embedding's multiplier (1 for none), in float32
     if (p != nullptr) v += to_f32(p[d]);
     o[d] = v;
   }
@@ -158,17 +158,17 @@ RL_EXPORT int rl_event_record(cudaEvent_t event, cudaStream_t stream) { return (
 
 RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* table,
                        const void* pos_table, float* out, int n_tokens, int hidden, int vocab,
-                       int n_positions, int* status, const int* feedback, int n_feedback,
+                       int n_positions, int* status, const int* feedback, int n_feedback, float scale,
                        cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 512 ? 256 : 128;
   if (dtype == RL_F32)
     rl::launch_pdl(rl::embed_kernel<float>, n_tokens, threads, 0, stream, ids, pos, (const float*)table,
-                   (const float*)pos_table, out, n_tokens, hidden, vocab, n_positions, status, feedback, n_feedback);
+                   (const float*)pos_table, out, n_tokens, hidden, vocab, n_positions, status, feedback, n_feedback, scale);
   else
     rl::launch_pdl(rl::embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, ids, pos,
                    (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, out, n_tokens, hidden, vocab,
-                   n_positions, status, feedback, n_feedback);
+                   n_positions, status, feedback, n_feedback, scale);
   RL_CHECK_LAUNCH();
   return 0;
 }

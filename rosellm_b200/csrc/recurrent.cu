@@ -9,6 +9,18 @@
 //   1, a gated linear recurrence with one gate for forgetting and writing: f = l + (1 - l) *
 //     sigmoid(f' + f_bias), w = f, k = 1 - f, r = silu(q'), no removal.  Output: each head's o RMS-normed with
 //     a weight per column that the heads share.
+//   2, linear attention with a decay per key channel: w = sigmoid(z)^(1/tau) with z = w0 + W2 p (p: a low-rank
+//     projection of the layer's input, no function in between), evaluated as exp(logsigmoid(z) / tau); k as it
+//     comes, r = q' * qscale, no removal.  Output: each head's o RMS-normed with a weight per column that the
+//     heads share, times silu(g).
+//   3, a matrix memory with exponential gates and a running maximum m per head (kept beside the state, zero
+//     at the start): i = cap * tanh((i' + i_bias) / cap), f = logsigmoid(cap * tanh((f' + f_bias) / cap)),
+//     m_t = max(f + m_(t-1), i), w = exp(f + m_(t-1) - m_t) for every channel, k = exp(i - m_t) k', r = q' * qscale.
+//     The normaliser n_t = w n_(t-1) + k is one more column of the state, whose value is 1 for every token, so
+//     the state has dv = (value size + 1) columns and n . r arrives as the output's last column.  Output:
+//     o / (max(|n . r|, exp(-m_t)) + floor_eps), each head's divided by its root mean square, times a weight
+//     per (head, column), times sigmoid(g).  `recurrence_gate_scan_kernel`, a warp a (request, head), walks the
+//     tokens in their order for m_t and leaves (w, exp(i - m_t), exp(-m_t)) per (token, head).
 //
 // The inputs are columns of one float32 matrix (the packed projections of the layer's input).  Three kernels:
 //   `recurrence_prep_kernel`, a block a token: everything that does not depend on the state (sigmoids,
@@ -41,9 +53,58 @@ struct RecurParams {
   float* oraw;  // [tokens, heads * dv]
   int n_tokens, n_heads, dk, dv, dkp, dvp, rec;
   float eps, decay_scale, unit_eps;
+  long state_stride;  // floats a slot
+  int m_off;          // (3) where a slot's running maxima [heads] begin
+  int dv_in;          // value columns a head in proj (dv, or dv - 1 for the form whose last column is the normaliser)
+  float tau_inv, cap, floor_eps, qscale;
+  float* gates;       // (3) [tokens, heads, 4]: w, exp(i - m_t), exp(-m_t)
 };
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// The running maximum of the matrix memory and what follows from it, token by token in order (so that the
+// numbers do not depend on how a prompt was cut): a warp a (request, head), 32 tokens' gates worked out at
+// once, then walked in turn.
+__global__ __launch_bounds__(128) void recurrence_gate_scan_kernel(const RecurParams p) {
+  pdl_begin();
+  const int req = blockIdx.x, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (head >= p.n_heads) return;
+  const int slot = p.slots[req];
+  if (slot < 0) return;
+  const int t0 = p.q_start[req], t1 = p.q_start[req + 1];
+  float* mp = p.state + (size_t)slot * p.state_stride + p.m_off + head;
+  float m = *mp;
+  const float bi = p.a_bias[head], bf = p.w0[head];
+  for (int base = t0; base < t1; base += 32) {
+    const int t = base + lane;
+    float gi = 0.f, gf = 0.f;
+    if (t < t1) {
+      const float* row = p.proj + (size_t)t * p.ldp;
+      gi = p.cap * tanhf((row[p.off_a + head] + bi) / p.cap);
+      gf = logsigmoidf_(p.cap * tanhf((row[p.off_w + head] + bf) / p.cap));
+    }
+    float m_before = 0.f, m_after = 0.f;
+    const int n = min(32, t1 - base);
+    for (int j = 0; j < n; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
+      const float m_new = fmaxf(fj + m, ij);
+      if (lane == j) {
+        m_before = m;
+        m_after = m_new;
+      }
+      m = m_new;
+    }
+    if (t < t1) {
+      float* g = p.gates + ((size_t)t * p.n_heads + head) * 4;
+      g[0] = expf(gf + m_before - m_after);
+      g[1] = expf(gi - m_after);
+      g[2] = expf(-m_after);
+    }
+  }
+  if (lane == 0) *mp = m;
+}
 
 // A block takes one token and `heads_per_block` heads.  Dynamic shared memory (MODE 0): tanh of the low-rank
 // input [rank], then k and a of the block's channels [heads_per_block * dk] each.
@@ -91,17 +152,35 @@ __global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams 
       }
     }
   } else {
+    if (MODE == 2) {  // the low-rank input of the decay, as it comes
+      for (int r = threadIdx.x; r < p.rank; r += blockDim.x) prep_s[r] = row[p.off_w + r];
+      __syncthreads();
+    }
     for (int c = h0 * dkp + threadIdx.x; c < h1 * dkp; c += blockDim.x) {
       const int head = c / dkp, i = c - head * dkp;
       float w = 0.f, k = 0.f, r = 0.f;
       if (i < dk) {
         const int ch = head * dk + i;
-        const float l = p.w0[ch];
-        const float f = l + (1.0f - l) * sigmoidf_(row[p.off_a + ch] + p.a_bias[ch]);
-        const float q = row[p.off_r + ch];
-        w = f;
-        k = 1.0f - f;
-        r = q * sigmoidf_(q);
+        if (MODE == 1) {
+          const float l = p.w0[ch];
+          const float f = l + (1.0f - l) * sigmoidf_(row[p.off_a + ch] + p.a_bias[ch]);
+          const float q = row[p.off_r + ch];
+          w = f;
+          k = 1.0f - f;
+          r = q * sigmoidf_(q);
+        } else if (MODE == 2) {
+          float z = p.w0[ch];
+#pragma unroll 8
+          for (int q = 0; q < p.rank; ++q) z = fmaf(p.w2t[(size_t)q * C + ch], prep_s[q], z);
+          w = expf(logsigmoidf_(z) * p.tau_inv);
+          k = row[p.off_k + ch];
+          r = row[p.off_r + ch] * p.qscale;
+        } else {
+          const float* g = p.gates + ((size_t)tok * p.n_heads + head) * 4;
+          w = g[0];
+          k = g[1] * row[p.off_k + ch];
+          r = row[p.off_r + ch] * p.qscale;
+        }
       }
       float* rec = record(head);
       rec[i] = w;
@@ -112,7 +191,10 @@ __global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams 
   constexpr int NV = MODE == 0 ? 5 : 3;
   for (int c = h0 * p.dvp + threadIdx.x; c < h1 * p.dvp; c += blockDim.x) {
     const int head = c / p.dvp, j = c - head * p.dvp;
-    record(head)[NV * dkp + j] = j < p.dv ? row[p.off_v + head * p.dv + j] : 0.f;
+    float v = 0.f;
+    if (j < p.dv_in) v = row[p.off_v + head * p.dv_in + j];
+    else if (j < p.dv) v = 1.0f;  // the normaliser's column
+    record(head)[NV * dkp + j] = v;
   }
 }
 
@@ -153,7 +235,7 @@ __global__ __launch_bounds__(REC_THREADS) void recurrence_seq_kernel(const Recur
   const int dk = p.dk, dv = p.dv, rec = p.rec;
   const int col = blockIdx.z * cols + threadIdx.x / TPC, part = threadIdx.x % TPC;
   float S[DKQ];
-  float* st = p.state + (((size_t)slot * p.n_heads + head) * dk) * dv;
+  float* st = p.state + (size_t)slot * p.state_stride + ((size_t)head * dk) * dv;
 #pragma unroll
   for (int k = 0; k < DKQ; ++k) {
     const int r = (k >> 2) * 4 * TPC + 4 * part + (k & 3);
@@ -269,22 +351,35 @@ __global__ __launch_bounds__(REC_THREADS) void recurrence_seq_kernel(const Recur
 template <int MODE, typename TOut>
 __global__ __launch_bounds__(256) void recurrence_out_kernel(const RecurParams p) {
   pdl_begin();
-  const int tok = blockIdx.x, dv = p.dv;
+  const int tok = blockIdx.x, dvs = p.dv, dv = p.dv_in;  // columns of the state, and those that are values
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const float* row = p.proj + (size_t)tok * p.ldp;
   for (int head = warp; head < p.n_heads; head += n_warps) {
-    const float* o = p.oraw + (size_t)tok * p.n_heads * dv + (size_t)head * dv;
+    const float* o = p.oraw + (size_t)tok * p.n_heads * dvs + (size_t)head * dvs;
+    float div = 1.0f;
+    if (MODE == 3) {
+      const float em = p.gates[((size_t)tok * p.n_heads + head) * 4 + 2];
+      div = 1.0f / (fmaxf(fabsf(o[dv]), em) + p.floor_eps);
+    }
     float ss = 0.f;
-    for (int c = lane; c < dv; c += 32) ss = fmaf(o[c], o[c], ss);
+    for (int c = lane; c < dv; c += 32) {
+      const float v = o[c] * div;
+      ss = fmaf(v, v, ss);
+    }
     ss = warp_sum(ss);
     const float rn = 1.0f / sqrtf(ss / (float)dv + p.eps);
     TOut* orow = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)head * dv;
     for (int c = lane; c < dv; c += 32) {
-      float v = o[c] * rn;
-      if (MODE == 0)
+      float v = o[c] * div * rn;
+      if (MODE == 0 || MODE == 3) {
         v = v * p.out_weight[head * dv + c] * sigmoidf_(row[p.off_g + head * dv + c]);
-      else
+      } else {
         v = v * p.out_weight[c];
+        if (MODE == 2) {
+          const float g = row[p.off_g + head * dv + c];
+          v *= g * sigmoidf_(g);
+        }
+      }
       orow[c] = from_f32<TOut>(v);
     }
   }
@@ -345,7 +440,7 @@ static void dispatch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) 
 // The padded key size of a record's vectors (16, 32, 64, 128 or 256), the padded value size, and the floats a
 // record takes: what the caller sizes `prep` by (heads * tokens * record floats).
 RL_EXPORT int rl_recurrence_record(int mode, int dk, int dv, int* dkp, int* dvp, int* rec) {
-  if (mode < 0 || mode > 1 || dk <= 0 || dk > 256 || dv <= 0 || dv > 256) return -2;
+  if (mode < 0 || mode > 3 || dk <= 0 || dk > 256 || dv <= 0 || dv > 257 || (dv > 256 && mode != 3)) return -2;
   int k = 16;
   while (k < dk) k *= 2;
   *dkp = k;
@@ -354,36 +449,58 @@ RL_EXPORT int rl_recurrence_record(int mode, int dk, int dv, int* dkp, int* dvp,
   return 0;
 }
 
-// mode 0: generalized delta rule; 1: gated recurrence (see the top of this file).  proj: float32 [tokens, ldp]
-// holding the projections at the given column offsets; state: float32 [slots, heads, dk, dv], read and written
-// for the step's requests (slot < 0: skipped); out: [tokens, heads * dv] of out_dtype, row stride ldo.
-// prep: float32 scratch [heads * tokens * record]; oraw: float32 scratch [tokens, heads * dv].
+// mode 0: generalized delta rule; 1: gated recurrence; 2: linear attention with decaying key channels; 3: matrix
+// memory (see the top of this file).  proj: float32 [tokens, ldp] holding the projections at the given column
+// offsets (3: off_a the input gate's and off_w the forget gate's logits, one column a head; a_bias and w0 their
+// biases [heads]); state: float32, `state_stride` floats a slot, of which the first heads * dk * dv are the
+// matrices (3: dv is the value size + 1, and the heads' running maxima lie at `m_off`), read and written for the
+// step's requests (slot < 0: skipped); out: [tokens, heads * value size] of out_dtype, row stride ldo.
+// prep: float32 scratch [heads * tokens * record]; oraw: float32 scratch [tokens, heads * dv]; gates (3): float32
+// scratch [tokens * heads * 4].
 RL_EXPORT int rl_recurrence(int mode, int out_dtype, const float* proj, long ldp, int off_r, int off_k, int off_v,
                             int off_a, int off_g, int off_w, const float* a_bias, const float* w0, const float* w2t,
                             int rank, const float* out_weight, float* state, void* out, long ldo, const int* q_start,
                             const int* slots, float* prep, float* oraw, int n_tokens, int n_reqs, int n_heads, int dk,
-                            int dv, float eps, float decay_scale, float unit_eps, cudaStream_t stream) {
+                            int dv, float eps, float decay_scale, float unit_eps, long state_stride, int m_off,
+                            float tau, float cap, float floor_eps, float qscale, float* gates, cudaStream_t stream) {
   if (n_reqs <= 0 || n_tokens <= 0) return 0;
   int dkp, dvp, rec;
   if (rl_recurrence_record(mode, dk, dv, &dkp, &dvp, &rec) != 0 || n_heads <= 0 || n_heads > 65535 || rank < 0) return -2;
+  if (state_stride < (long)n_heads * dk * dv) return -2;
+  if (mode == 2 && (tau <= 0.f || w2t == nullptr || rank <= 0)) return -2;
+  if (mode == 3 && (cap <= 0.f || gates == nullptr || dv < 2 || m_off < n_heads * dk * dv || m_off + n_heads > state_stride))
+    return -2;
   rl::RecurParams p{proj, ldp, off_r, off_k, off_v, off_a, off_g, off_w, a_bias, w0, w2t, rank, out_weight, state, out,
-                    ldo, q_start, slots, prep, oraw, n_tokens, n_heads, dk, dv, dkp, dvp, rec, eps, decay_scale, unit_eps};
+                    ldo, q_start, slots, prep, oraw, n_tokens, n_heads, dk, dv, dkp, dvp, rec, eps, decay_scale, unit_eps,
+                    state_stride, m_off, mode == 3 ? dv - 1 : dv, mode == 2 ? 1.0f / tau : 0.f, cap, floor_eps, qscale, gates};
   // heads a block of the preparation: about 256 channels (a thread a channel), fewer with many tokens' worth of blocks anyway
   int hpb = 256 / dk;
   hpb = hpb < 1 ? 1 : (hpb > n_heads ? n_heads : hpb);
   const dim3 prep_grid(n_tokens, (n_heads + hpb - 1) / hpb);
-  const size_t prep_smem = mode == 0 ? ((size_t)rank + 2 * (size_t)hpb * dk) * sizeof(float) : 0;
+  const size_t prep_smem = mode == 0 ? ((size_t)rank + 2 * (size_t)hpb * dk) * sizeof(float)
+                                     : (mode == 2 ? (size_t)rank * sizeof(float) : 0);
   if (prep_smem > 48 * 1024) return -2;
   if (mode == 0) {
     rl::launch_pdl(rl::recurrence_prep_kernel<0>, prep_grid, 256, prep_smem, stream, p, hpb);
     rl::dispatch_seq<0>(p, n_reqs, stream);
     if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<0, float>, n_tokens, 256, 0, stream, p);
     else rl::launch_pdl(rl::recurrence_out_kernel<0, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
-  } else {
+  } else if (mode == 1) {
     rl::launch_pdl(rl::recurrence_prep_kernel<1>, prep_grid, 256, 0, stream, p, hpb);
     rl::dispatch_seq<1>(p, n_reqs, stream);
     if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<1, float>, n_tokens, 256, 0, stream, p);
     else rl::launch_pdl(rl::recurrence_out_kernel<1, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
+  } else if (mode == 2) {  // the sequential kernel is the one of the form without removal
+    rl::launch_pdl(rl::recurrence_prep_kernel<2>, prep_grid, 256, prep_smem, stream, p, hpb);
+    rl::dispatch_seq<1>(p, n_reqs, stream);
+    if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<2, float>, n_tokens, 256, 0, stream, p);
+    else rl::launch_pdl(rl::recurrence_out_kernel<2, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
+  } else {
+    rl::launch_pdl(rl::recurrence_gate_scan_kernel, dim3(n_reqs, (n_heads + 3) / 4), 128, 0, stream, p);
+    rl::launch_pdl(rl::recurrence_prep_kernel<3>, prep_grid, 256, 0, stream, p, hpb);
+    rl::dispatch_seq<1>(p, n_reqs, stream);
+    if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<3, float>, n_tokens, 256, 0, stream, p);
+    else rl::launch_pdl(rl::recurrence_out_kernel<3, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
   }
   RL_CHECK_LAUNCH();
   return 0;

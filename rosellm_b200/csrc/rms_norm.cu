@@ -128,6 +128,47 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __r
   if (i < n) out[i] = __float2bfloat16_rn(x[i]);
 }
 
+// stream[i] = rmsnorm(alpha * stream[i] + sigmoid(z[i]) * (s0 * y0[i] + s1 * y1[i])) * gamma: the norm AFTER the sum
+// of a layer that normalises the stream itself, with the sublayer's result (of one mixer, or of two side by
+// side with a weight each) passing a gate whose logits z the caller computed from the sublayer's input.  The new
+// row also goes out in bfloat16 (copy) for the products of the next sublayer.  The row is kept in shared memory
+// between the statistic and the scaling where it fits (KEEP), else worked out a second time.
+template <bool KEEP>
+__global__ __launch_bounds__(256) void gated_join_norm_kernel(const float* __restrict__ y0, long ld0, float s0,
+                                                              const float* __restrict__ y1, long ld1, float s1,
+                                                              const float* __restrict__ z, long ldz,
+                                                              const float* __restrict__ gamma, float* __restrict__ stream,
+                                                              long lds, __nv_bfloat16* __restrict__ copy, long ldc,
+                                                              int n_rows, int width, float eps, float alpha) {
+  extern __shared__ float join_row_s[];
+  __shared__ float scratch[33];
+  pdl_begin();
+  const int i = blockIdx.x;
+  if (i >= n_rows) return;
+  float* xr = stream + (size_t)i * lds;
+  const float* a = y0 + (size_t)i * ld0;
+  const float* b = y1 != nullptr ? y1 + (size_t)i * ld1 : nullptr;
+  const float* zr = z != nullptr ? z + (size_t)i * ldz : nullptr;  // no logits: no gate
+  auto joined = [&](int d) {
+    float y = s0 * a[d];
+    if (b != nullptr) y = fmaf(s1, b[d], y);
+    const float g = zr != nullptr ? 1.0f / (1.0f + expf(-zr[d])) : 1.0f;
+    return fmaf(alpha, xr[d], g * y);
+  };
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = joined(d);
+    if (KEEP) join_row_s[d] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {  // a thread meets the entries it wrote itself
+    const float v = (KEEP ? join_row_s[d] : joined(d)) * r * gamma[d];
+    xr[d] = v;
+    if (copy != nullptr) copy[(size_t)i * ldc + d] = __float2bfloat16_rn(v);
+  }
+}
+
 static inline int norm_threads(int width) {
   int t = (width + 3) / 4;
   t = (t + 31) / 32 * 32;
@@ -186,6 +227,25 @@ RL_EXPORT int rl_rmsnorm_add_norm(int out_dtype, const float* y, long ldy, const
   else
     rl::launch_pdl(rl::rmsnorm_add_norm_kernel<__nv_bfloat16>, n_rows, rl::norm_threads(width), smem, stream, y, ldy,
                    gamma, stream_rows, lds, gamma_next, (__nv_bfloat16*)next, ldn, n_rows, width, eps, eps_next);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// stream = rmsnorm(alpha * stream + sigmoid(z) * (s0 * y0 + s1 * y1)) * gamma (y1 may be null; z null: no gate), with an optional
+// bfloat16 copy of the new rows; see the kernel.
+RL_EXPORT int rl_gated_join_norm(const float* y0, long ld0, float s0, const float* y1, long ld1, float s1, const float* z,
+                                 long ldz, const float* gamma, float* stream_rows, long lds, void* copy, long ldc,
+                                 int n_rows, int width, float eps, float alpha, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (width <= 0 || y0 == nullptr) return -2;
+  const int threads = rl::norm_threads(width);
+  const size_t row_bytes = (size_t)width * sizeof(float);
+  if (row_bytes <= 40 * 1024)
+    rl::launch_pdl(rl::gated_join_norm_kernel<true>, n_rows, threads, row_bytes, stream, y0, ld0, s0, y1, ld1, s1, z, ldz,
+                   gamma, stream_rows, lds, (__nv_bfloat16*)copy, ldc, n_rows, width, eps, alpha);
+  else
+    rl::launch_pdl(rl::gated_join_norm_kernel<false>, n_rows, threads, 0, stream, y0, ld0, s0, y1, ld1, s1, z, ldz, gamma,
+                   stream_rows, lds, (__nv_bfloat16*)copy, ldc, n_rows, width, eps, alpha);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -111,15 +111,17 @@ class Model:
 
     # ---- what the cache manager has to provide --------------------------------
     def kv_specs(self) -> dict:
-        """``KVCacheSpec`` of every sub-part that keeps keys and values, by cache key (the layer's
-        index for the sub-part called ``mixer``, ``(layer, name)`` for any other)."""
+        """``KVCacheSpec`` of every sub-part that keeps keys and values, by cache key (the run's own
+        number, which is the layer's index unless the run is an instance, for the sub-part called
+        ``mixer``; ``(number, name)`` for any other)."""
         out = {}
-        writers = {e.layer for e in self.spec.run_order if e.writes_cache}
-        for i, layer in enumerate(self.layers):
-            for name, part in layer.parts.items():
+        for e in self.spec.run_order:
+            if not e.writes_cache:
+                continue
+            for name, part in self.layers[e.layer].parts.items():
                 cs = part.cache_spec()
-                if cs is not None and i in writers:
-                    out[_cache_key(i, name)] = cs
+                if cs is not None:
+                    out[_cache_key(e.own_key, name)] = cs
         for pos, e in enumerate(self.spec.run_order):
             if e.writes_cache:
                 continue
@@ -134,16 +136,17 @@ class Model:
 
     def state_specs(self) -> dict:
         """``StateSpec`` of every part that keeps per-request state: a layer's sub-parts by their cache
-        key, the embedding (the last token of a request, say) under ``"embedding"``."""
+        key (one set per run of the layer that keeps state of its own), the embedding (the last token of a
+        request, say) under ``"embedding"``."""
         out = {}
         ss = self.embedding.state_spec()
         if ss is not None:
             out["embedding"] = ss
-        for i, layer in enumerate(self.layers):
-            for name, part in layer.parts.items():
+        for e in self.spec.run_order:
+            for name, part in self.layers[e.layer].parts.items():
                 ss = part.state_spec()
                 if ss is not None:
-                    out[_cache_key(i, name)] = ss
+                    out[_cache_key(e.own_key, name)] = ss
         return out
 
     @property

@@ -124,7 +124,7 @@ def _lib() -> ctypes.CDLL:
     lib = build.load()
     if not _signatures_set:
         P, I, L, F = c_void_p, c_int, c_long, c_float
-        lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P, I, P]
+        lib.rl_embed.argtypes = [I, P, P, P, P, P, I, I, I, I, P, P, I, F, P]
         lib.rl_layernorm.argtypes = [I, P, P, P, P, P, I, I, F, P]
         lib.rl_gemm_simt.argtypes = [I, I, P, L, P, P, P, L, I, I, I, I, I, I, P, P, I, P, P, P,
                                      I, I, I, I, I, I, P, P]
@@ -169,17 +169,20 @@ def _lib() -> ctypes.CDLL:
         lib.rl_moe_experts.argtypes = [I, P, L, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, F, F, I, P]
         lib.rl_embed_pair.argtypes = [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P, P, I, P]
         lib.rl_rmsnorm_add_norm.argtypes = [I, P, L, P, P, L, P, P, L, I, I, F, F, P]
-        lib.rl_recurrence.argtypes = [I, I, P, L, I, I, I, I, I, I, P, P, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, F, F, F, P]
+        lib.rl_recurrence.argtypes = [I, I, P, L, I, I, I, I, I, I, P, P, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, F, F, F,
+                                      L, I, F, F, F, F, P, P]
         lib.rl_recurrence_record.argtypes = [I, I, I, P, P, P]
         lib.rl_bias_attention_shape.argtypes = [I, I, P, P]
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
-                                          F, F, I, P, P, I, P, P, I, P]
+                                          F, F, I, P, P, I, P, P, I, I, P, P]
+        lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, F, P]
+        lib.rl_gated_join_norm.argtypes = [P, L, F, P, L, F, P, L, P, P, L, P, L, I, I, F, F, P]
         lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
                      "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts", "rl_embed_pair",
                      "rl_rmsnorm_add_norm", "rl_recurrence", "rl_recurrence_record", "rl_bias_attention_shape", "rl_bias_attention",
-                     "rl_bias_kv_store"):
+                     "rl_bias_kv_store", "rl_qkv_norm_rotate", "rl_gated_join_norm"):
             getattr(lib, name).restype = I
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
@@ -284,8 +287,8 @@ def record_event(event: "torch.cuda.Event") -> None:
         raise KernelError(f"record_event: CUDA error {rc}")
 
 
-def embed(token_ids, positions, table, pos_table, out, feedback=None) -> None:
-    """out[n] = table[token_ids[n]] (+ pos_table[positions[n]]), float32 [tokens, hidden].
+def embed(token_ids, positions, table, pos_table, out, feedback=None, scale: float = 1.0) -> None:
+    """out[n] = scale * table[token_ids[n]] (+ pos_table[positions[n]]), float32 [tokens, hidden].
     With ``feedback`` (int32), an id -(r+1) is replaced on the device by ``feedback[r]``."""
     _need(token_ids, "token_ids", torch.int32)
     _need(table, "table")
@@ -300,7 +303,7 @@ def embed(token_ids, positions, table, pos_table, out, feedback=None) -> None:
         n_pos = pos_table.shape[0]
     rc = _lib().rl_embed(_code(table), _ptr(token_ids), _ptr(positions), _ptr(table), _ptr(pos_table),
                          _ptr(out), n, hidden, table.shape[0], n_pos, _ptr(status_word(out.device)),
-                         _ptr(feedback), 0 if feedback is None else feedback.numel(), _stream())
+                         _ptr(feedback), 0 if feedback is None else feedback.numel(), float(scale), _stream())
     _ok(rc, "embed")
 
 
@@ -1229,7 +1232,7 @@ RMSNORM_ADD_NORM_MAX_WIDTH = 48 * 1024 // 4 - 64
 
 # ---- mixers with a matrix-valued state -------------------------------------------------------------
 
-RECURRENCES = {"delta": 0, "gated": 1}
+RECURRENCES = {"delta": 0, "gated": 1, "decayed_keys": 2, "matrix_memory": 3}
 
 
 def recurrence_record(mode: int, dk: int, dv: int) -> int:
@@ -1242,13 +1245,19 @@ def recurrence_record(mode: int, dk: int, dv: int) -> int:
 
 def recurrence(mode: int, proj, offsets: dict, state, out, q_start, slots, prep, oraw, *, n_reqs: int, n_heads: int,
                dk: int, dv: int, eps: float, a_bias, w0, out_weight, w2t=None, rank: int = 0, decay_scale: float = 0.0,
-               unit_eps: float = 0.0) -> None:
+               unit_eps: float = 0.0, tau: float = 0.0, cap: float = 0.0, floor_eps: float = 0.0, qscale: float = 1.0,
+               gates=None) -> None:
     """One step of a recurrence over matrix states (csrc/recurrent.cu) for every request of the step.
     ``proj`` float32 [tokens, columns]: the packed projections, ``offsets`` the first column of
     ``r``, ``k``, ``v``, ``a``, ``g``, ``w`` (those the form has); ``state`` float32
     [slots, heads, dk, dv]; ``out`` [tokens, heads * dv] float32 or bfloat16; ``prep`` float32 scratch of
     heads * tokens * ``recurrence_record`` floats, ``oraw`` float32 scratch [tokens, heads * dv];
-    ``w2t`` float32 [rank, heads * dk]: the low-rank decay's second matrix, transposed."""
+    ``w2t`` float32 [rank, heads * dk]: the low-rank decay's second matrix, transposed.
+    The matrix memory (mode 3) keeps its normaliser as one more column of the state and a running maximum a
+    head behind the matrices: ``state`` float32 [slots, heads * dk * (dv + 1) + heads]; ``gates`` float32 scratch
+    of tokens * heads * 4 floats; ``cap`` bounds the gates' logits, ``floor_eps`` is added to the output's divisor;
+    ``a_bias`` / ``w0`` are the input and forget gates' biases [heads].  ``tau`` (mode 2): the decay is
+    sigmoid(.)^(1/tau); ``qscale`` (modes 2, 3) multiplies the queries."""
     _need(proj, "proj", torch.float32, contiguous=False)
     _need(state, "state", torch.float32)
     _need(out, "out", contiguous=False)
@@ -1261,23 +1270,31 @@ def recurrence(mode: int, proj, offsets: dict, state, out, q_start, slots, prep,
         _need(w2t, "w2t", torch.float32)
         if tuple(w2t.shape) != (rank, n_heads * dk):
             raise KernelError("recurrence: the low-rank matrix has another shape")
-    if tuple(state.shape[1:]) != (n_heads, dk, dv) or out.shape[1] != n_heads * dv or proj.stride(1) != 1 \
+    dvs = dv + 1 if mode == 3 else dv  # columns of a head's state
+    want_state = (n_heads * dk * dvs + n_heads,) if mode == 3 else (n_heads, dk, dv)
+    if tuple(state.shape[1:]) != want_state or out.shape[1] != n_heads * dv or proj.stride(1) != 1 \
             or out.stride(1) != 1 or out.shape[0] != n_tokens:
         raise KernelError("recurrence: shapes do not fit")
-    if prep.numel() < n_heads * n_tokens * recurrence_record(mode, dk, dv) or oraw.numel() < n_tokens * n_heads * dv:
+    if prep.numel() < n_heads * n_tokens * recurrence_record(mode, dk, dvs) or oraw.numel() < n_tokens * n_heads * dvs:
         raise KernelError("recurrence: scratch too small")
+    if mode == 2 and (w2t is None or rank <= 0 or tau <= 0):
+        raise KernelError("recurrence: the form with decaying key channels needs its low-rank decay and tau")
+    if mode == 3:
+        if gates is None or gates.dtype != torch.float32 or gates.numel() < n_tokens * n_heads * 4 or cap <= 0:
+            raise KernelError("recurrence: the matrix memory needs its gates' scratch and a positive cap")
     if mode == 0 and (w2t is None or rank <= 0):
         raise KernelError("recurrence: the delta form needs its low-rank decay")
     off = [int(offsets.get(k, -1)) for k in ("r", "k", "v", "a", "g", "w")]
     rc = _lib().rl_recurrence(int(mode), _code(out), _ptr(proj), proj.stride(0), *off, _ptr(a_bias), _ptr(w0), _ptr(w2t),
                               int(rank), _ptr(out_weight), _ptr(state), _ptr(out), out.stride(0), _ptr(q_start),
-                              _ptr(slots), _ptr(prep), _ptr(oraw), n_tokens, n_reqs, n_heads, dk, dv, float(eps),
-                              float(decay_scale), float(unit_eps), _stream())
+                              _ptr(slots), _ptr(prep), _ptr(oraw), n_tokens, n_reqs, n_heads, dk, dvs, float(eps),
+                              float(decay_scale), float(unit_eps), state.stride(0), n_heads * dk * dvs, float(tau),
+                              float(cap), float(floor_eps), float(qscale), _ptr(gates), _stream())
     if rc == -2:
         raise KernelError(f"recurrence: sizes not taken (key size {dk}, value size {dv}: up to 256 each)")
     _ok(rc, "recurrence")
     global _launches
-    _launches += 2
+    _launches += 3 if mode == 3 else 2
 
 
 # ---- attention with a distance bias over rows of [key | value] -------------------------------------
@@ -1332,14 +1349,16 @@ def bias_kv_store(k, v, pool, block_table, positions, req_of_token, slots, *, v_
 def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, dk: int, dv: int, v_at: int,
                    scale: float, slopes=None, temp_coef: float = 0.0, temp_every: int = 0, tiles=None, n_tiles: int = 0,
                    tile_tokens: int = 16, decode_reqs=None, n_decode: int = 0, max_pos: int, n_splits: int = 1, part_o=None,
-                   part_ml=None, tensor_cores: bool = False) -> None:
+                   part_ml=None, tensor_cores: bool = False, window: int = 0, head_scale=None) -> None:
     """Causal attention of the step's queries over the cached rows (csrc/bias_attention.cu).
     ``tensor_cores``: prompt portions on mma.sync (bfloat16 pool and output, sizes up to 128; the tiles cut as
     ``bias_attention_shape(.., True)`` says).
     ``n_splits`` > 1: the keys of every decoded request are cut into so many parts (``part_o`` float32
     [n_decode * heads * n_splits, dv] and ``part_ml`` [.., 2] are their scratch) and merged in order.
     ``q`` float32 [tokens, heads * dk] and ``gate`` float32 [tokens, heads * dv] (or ``None``) may be views
-    with a row stride; ``out`` [tokens, heads * dv] float32 or bfloat16; ``slopes`` float32 [heads] or ``None``."""
+    with a row stride; ``out`` [tokens, heads * dv] float32 or bfloat16; ``slopes`` float32 [heads] or ``None``.
+    ``window`` > 0: a query sees itself and the ``window - 1`` keys before it; ``head_scale`` float32 [heads]: a
+    further factor of every score of a head."""
     _need(q, "q", torch.float32, contiguous=False)
     _need(out, "out", contiguous=False)
     _need(pool, "pool")
@@ -1350,10 +1369,11 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
         _need(gate, "gate", torch.float32, contiguous=False)
         if gate.shape[1] != n_heads * dv or gate.stride(1) != 1:
             raise KernelError("bias_attention: the gate has another shape")
-    if slopes is not None:
-        _need(slopes, "slopes", torch.float32)
-        if slopes.numel() != n_heads:
-            raise KernelError("bias_attention: one slope a head")
+    for t, name in ((slopes, "slopes"), (head_scale, "head_scale")):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != n_heads:
+                raise KernelError(f"bias_attention: {name} has one entry a head")
     global _launches
     if n_decode <= 0:
         n_splits = 1
@@ -1369,8 +1389,61 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
                                   min(block_table.shape[1], -(-max_pos // page_size)), float(scale), float(temp_coef),
                                   int(temp_every), _ptr(slopes), _ptr(status_word(out.device)), int(n_splits), _ptr(part_o),
                                   _ptr(part_ml), int(bool(tensor_cores) and bias_attention_tensor_cores(pool.dtype, dk, dv)
-                                                     and out.dtype == torch.bfloat16), _stream())
+                                                     and out.dtype == torch.bfloat16), int(window), _ptr(head_scale),
+                                  _stream())
     if rc in (-2, -3, -4):
         raise KernelError(f"bias_attention: sizes not taken (code {rc}: key and value sizes up to 256; tiles a multiple "
                           "of the tokens a block takes)")
     _ok(rc, "bias_attention")
+
+
+def qkv_norm_rotate(q, k, v, positions, *, n_heads: int, n_kv: int, dk: int, dv: int, eps: float, q_norm=None, k_norm=None,
+                    freq=None, rot_dims: int = 0, unit_values: bool = False) -> None:
+    """In place on float32 views (row strides allowed): every head of ``q`` [tokens, heads * dk] and ``k``
+    [tokens, kv heads * dk] divided by its root mean square and multiplied by ``q_norm`` / ``k_norm`` (float32
+    [dk], both or neither), then its first ``rot_dims`` entries turned in neighbouring pairs by position *
+    ``freq[i]``; with ``unit_values`` every head of ``v`` [tokens, kv heads * dv] divided by its root mean square."""
+    for t, name, width in ((q, "q", n_heads * dk), (k, "k", n_kv * dk), (v, "v", n_kv * dv)):
+        _need(t, name, torch.float32, contiguous=False)
+        if t.shape[1] != width or t.stride(1) != 1 or t.shape[0] != q.shape[0]:
+            raise KernelError(f"qkv_norm_rotate: {name} has another shape")
+    for t, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != dk:
+                raise KernelError(f"qkv_norm_rotate: {name} has one entry a key channel")
+    if rot_dims:
+        _need(freq, "freq", torch.float32)
+        if freq.numel() < rot_dims // 2:
+            raise KernelError("qkv_norm_rotate: one frequency a turned pair")
+    rc = _lib().rl_qkv_norm_rotate(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(q_norm), _ptr(k_norm),
+                                   _ptr(freq) if rot_dims else None, _ptr(positions), q.shape[0], n_heads, n_kv, dk, dv,
+                                   int(rot_dims), int(bool(unit_values)), float(eps), _stream())
+    if rc == -2:
+        raise KernelError("qkv_norm_rotate: sizes not taken (an even number of turned entries, at most the key size; "
+                          "both norms or neither)")
+    _ok(rc, "qkv_norm_rotate")
+
+
+def gated_join_norm(y0, s0: float, y1, s1: float, z, gamma, eps: float, alpha: float, stream_rows, copy=None) -> None:
+    """stream = rmsnorm(alpha * stream + sigmoid(z) * (s0 * y0 + s1 * y1)) * gamma, row by row in float32 (``y1`` may be
+    ``None``; ``z`` ``None``: no gate); ``copy`` (bfloat16, or ``None``) receives the new rows rounded."""
+    n, width = stream_rows.shape
+    _need(stream_rows, "stream_rows", torch.float32)
+    _need(gamma, "gamma", torch.float32)
+    for t, name in ((y0, "y0"), (y1, "y1"), (z, "z")):
+        if t is None and name != "y0":
+            continue
+        _need(t, name, torch.float32, contiguous=False)
+        if tuple(t.shape) != (n, width) or t.stride(1) != 1:
+            raise KernelError(f"gated_join_norm: {name} has another shape")
+    if gamma.numel() != width:
+        raise KernelError("gated_join_norm: the norm's weight has another size")
+    if copy is not None:
+        _need(copy, "copy", torch.bfloat16)
+        if tuple(copy.shape) != (n, width):
+            raise KernelError("gated_join_norm: the copy has another shape")
+    rc = _lib().rl_gated_join_norm(_ptr(y0), y0.stride(0), float(s0), _ptr(y1), 0 if y1 is None else y1.stride(0), float(s1),
+                                   _ptr(z), 0 if z is None else z.stride(0), _ptr(gamma), _ptr(stream_rows), stream_rows.stride(0), _ptr(copy),
+                                   0 if copy is None else copy.stride(0), n, width, float(eps), float(alpha), _stream())
+    _ok(rc, "gated_join_norm")

@@ -164,3 +164,120 @@ class GatedRecurrenceMixer(_StateMixer):
                      ctx.q_start, ctx.slots, prep, oraw, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.key_dim,
                      dv=self.value_dim, eps=self.norm_eps, a_bias=self.f_bias, w0=self.lower, out_weight=self.out_norm)
         K.linear(buf, self.out_weight, None, x, residual=add)
+
+
+@register_part("mixer", "decayed_linear_attention")
+class DecayedLinearAttention(_StateMixer):
+    """Linear attention whose state forgets per key channel.  ``q = W_q h * query_scale`` (``None``:
+    key_dim^(-1/2)), ``k = W_k h`` (heads x key_dim), ``v = W_v h`` (heads x value_dim); a decay per head and key
+    channel ``a = sigmoid(z)^(1/tau)`` with ``z = W_a2 (W_a1 h) + a_bias``, a projection through a low rank with
+    no function in between; ``S_t = diag(a_t) S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t``.  Each head's ``o`` is
+    RMS-normed over value_dim with a weight the heads share (``norm_eps``), the merged heads are multiplied by
+    ``silu(W_g h)``, then ``W_o``.  ``low_rank``: the inner size of the decay's projection; ``None`` takes it
+    from the bound tensors.  The decay is evaluated as ``exp(logsigmoid(z) / tau)`` in float32."""
+
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, tau: float, norm_eps: float,
+                 low_rank: int | None = None, query_scale: float | None = None) -> None:
+        if key_dim > 256 or value_dim > 256:
+            raise ValueError(f"decayed linear attention: sizes {key_dim} / {value_dim}: the state kernel takes up to 256")
+        if tau <= 0:
+            raise ValueError("decayed linear attention: tau must be positive")
+        self.hidden_size, self.num_heads, self.key_dim, self.value_dim = hidden_size, num_heads, key_dim, value_dim
+        self.tau, self.norm_eps, self.low_rank = float(tau), float(norm_eps), low_rank
+        self.query_scale = float(key_dim) ** -0.5 if query_scale is None else float(query_scale)
+        self.key_width, self.out_width = num_heads * key_dim, num_heads * value_dim
+        self.out_padded = -(-self.out_width // 8) * 8
+        self.proj_weight = self.out_weight = None
+
+    def param_specs(self):
+        kw, vw, hid, rank = self.key_width, self.out_width, self.hidden_size, -1 if self.low_rank is None else self.low_rank
+        return [ParamSpec("q_weight", (kw, hid)), ParamSpec("k_weight", (kw, hid)), ParamSpec("v_weight", (vw, hid)),
+                ParamSpec("g_weight", (vw, hid)), ParamSpec("a1_weight", (rank, hid)),
+                ParamSpec("a2_weight", (kw, rank), kind="vector"), ParamSpec("a_bias", (kw,), kind="vector", init="zeros"),
+                ParamSpec("out_norm", (self.value_dim,), kind="vector", init="ones"), ParamSpec("out_weight", (hid, vw))]
+
+    def state_spec(self):
+        return StateSpec((self.num_heads, self.key_dim, self.value_dim), torch.float32)
+
+    def bind(self, tensors) -> None:
+        t = dict(tensors)
+        rank = t["a1_weight"].shape[0]
+        if t["a2_weight"].shape[1] != rank or (self.low_rank is not None and rank != self.low_rank):
+            raise ValueError(f"decayed linear attention: the decay's two matrices disagree on their inner size "
+                             f"({t['a1_weight'].shape[0]} and {t['a2_weight'].shape[1]})")
+        self.rank = rank
+        self.proj_weight, offs = pack_rows([t[n + "_weight"] for n in ("q", "k", "v", "g", "a1")])
+        self.offsets = dict(zip(("r", "k", "v", "g", "w"), offs))
+        self.a2t_weight = t["a2_weight"].t().contiguous()  # [rank, channels]: the kernel's threads walk the channels
+        self.a_bias, self.out_norm, self.out_weight = t["a_bias"], t["out_norm"], t["out_weight"]
+        self._pad_out_weight()
+
+    def forward(self, ctx, run, h, x, add: bool = True) -> None:
+        proj = self._project(ctx, h)
+        buf, view = self._out_buffer(ctx)
+        mode = K.RECURRENCES["decayed_keys"]
+        prep, oraw = self._scratch(ctx, mode, self.key_dim, self.value_dim)
+        K.recurrence(mode, proj, self.offsets, ctx.state(run.state_key), buf if view is None else view,
+                     ctx.q_start, ctx.slots, prep, oraw, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.key_dim,
+                     dv=self.value_dim, eps=self.norm_eps, a_bias=self.a_bias, w0=self.a_bias, out_weight=self.out_norm,
+                     w2t=self.a2t_weight, rank=self.rank, tau=self.tau, qscale=self.query_scale)
+        K.linear(buf, self.out_weight, None, x, residual=add)
+
+
+@register_part("mixer", "matrix_memory")
+class MatrixMemory(_StateMixer):
+    """A matrix memory with an exponential input gate, kept in range by a running maximum.  ``q = W_q h *
+    query_scale`` (``None``: key_dim^(-1/2)), ``k = W_k h`` (heads x key_dim), ``v = W_v h`` (heads x value_dim);
+    per head the log gates ``i = cap * tanh((W_i h + i_bias) / cap)`` and ``f = logsigmoid(cap * tanh((W_f h +
+    f_bias) / cap))`` (``gate_cap``).  With ``m_0 = 0``, ``S_0 = 0``, ``n_0 = 0``:
+
+        m_t = max(f + m_(t-1), i);  S_t = e^(f + m_(t-1) - m_t) S_(t-1) + e^(i - m_t) k v^T;  n_t likewise with k alone
+        o_t = S_t^T q / (max(|n_t . q|, e^(-m_t)) + floor_eps)
+
+    Each head's ``o`` is divided by its root mean square (``norm_eps``); the merged heads are multiplied by
+    ``out_norm`` (one entry per head and column) and by ``sigmoid(W_g h)``, then ``W_o``.
+
+    The state slot holds, per head, the matrix with the normaliser as one more column ([key_dim, value_dim +
+    1]: n obeys S's recurrence with a value of 1), and behind all matrices the heads' running maxima."""
+
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, gate_cap: float, norm_eps: float,
+                 floor_eps: float = 1e-6, query_scale: float | None = None) -> None:
+        if key_dim > 256 or value_dim > 256:
+            raise ValueError(f"matrix memory: sizes {key_dim} / {value_dim}: the state kernel takes up to 256")
+        if gate_cap <= 0:
+            raise ValueError("matrix memory: the gates' cap must be positive")
+        self.hidden_size, self.num_heads, self.key_dim, self.value_dim = hidden_size, num_heads, key_dim, value_dim
+        self.gate_cap, self.norm_eps, self.floor_eps = float(gate_cap), float(norm_eps), float(floor_eps)
+        self.query_scale = float(key_dim) ** -0.5 if query_scale is None else float(query_scale)
+        self.key_width, self.out_width = num_heads * key_dim, num_heads * value_dim
+        self.out_padded = -(-self.out_width // 8) * 8
+        self.proj_weight = self.out_weight = None
+
+    def param_specs(self):
+        kw, vw, hid, H = self.key_width, self.out_width, self.hidden_size, self.num_heads
+        return [ParamSpec("q_weight", (kw, hid)), ParamSpec("k_weight", (kw, hid)), ParamSpec("v_weight", (vw, hid)),
+                ParamSpec("g_weight", (vw, hid)), ParamSpec("i_weight", (H, hid)), ParamSpec("f_weight", (H, hid)),
+                ParamSpec("i_bias", (H,), kind="vector", init="zeros"), ParamSpec("f_bias", (H,), kind="vector", init="zeros"),
+                ParamSpec("out_norm", (vw,), kind="vector", init="ones"), ParamSpec("out_weight", (hid, vw))]
+
+    def state_spec(self):
+        return StateSpec((self.num_heads * self.key_dim * (self.value_dim + 1) + self.num_heads,), torch.float32)
+
+    def bind(self, tensors) -> None:
+        t = dict(tensors)
+        self.proj_weight, offs = pack_rows([t[n + "_weight"] for n in ("q", "k", "v", "g", "i", "f")])
+        self.offsets = dict(zip(("r", "k", "v", "g", "a", "w"), offs))
+        self.i_bias, self.f_bias, self.out_norm, self.out_weight = t["i_bias"], t["f_bias"], t["out_norm"], t["out_weight"]
+        self._pad_out_weight()
+
+    def forward(self, ctx, run, h, x, add: bool = True) -> None:
+        proj = self._project(ctx, h)
+        buf, view = self._out_buffer(ctx)
+        mode = K.RECURRENCES["matrix_memory"]
+        prep, oraw = self._scratch(ctx, mode, self.key_dim, self.value_dim + 1)
+        gates = ctx.workspace.get("state_mixer_gates", (ctx.n_tokens * self.num_heads * 4,), torch.float32)
+        K.recurrence(mode, proj, self.offsets, ctx.state(run.state_key), buf if view is None else view,
+                     ctx.q_start, ctx.slots, prep, oraw, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.key_dim,
+                     dv=self.value_dim, eps=self.norm_eps, a_bias=self.i_bias, w0=self.f_bias, out_weight=self.out_norm,
+                     cap=self.gate_cap, floor_eps=self.floor_eps, qscale=self.query_scale, gates=gates)
+        K.linear(buf, self.out_weight, None, x, residual=add)

@@ -105,17 +105,27 @@ class RunEntry:
     layer's own cache and appends the step's keys and values to it before reading.  With
     ``cache_of`` set (to another layer, or to the layer itself when it runs a second
     time) the run only reads that layer's cache, which an earlier run has filled.
+    ``instance`` set: the run uses the layer's parts and tensors but keeps pages and state of its
+    own under that number (a stack that repeats its layers' weights, each repetition with a cache
+    of its own); numbers of instances and of layers that run as themselves share one space, so an
+    instance takes a number that no such layer and no other instance has.
     """
 
     layer: int
     cache_of: int | None = None
+    instance: int | None = None
     # which of the layer's sub-parts this entry is handed to ("mixer" unless a block with
     # several mixers says otherwise through ``for_part``)
     part: str = "mixer"
 
     @property
+    def own_key(self) -> int:
+        """The number under which this run keeps what it keeps itself."""
+        return self.layer if self.instance is None else self.instance
+
+    @property
     def cache_layer(self) -> int:
-        return self.layer if self.cache_of is None else self.cache_of
+        return self.own_key if self.cache_of is None else self.cache_of
 
     # Keys under which the cache manager keeps a mixer's pages and state rows: the layer's
     # index for the sub-part called "mixer", (layer, name) for any other.
@@ -125,7 +135,7 @@ class RunEntry:
 
     @property
     def state_key(self):
-        return self.layer if self.part == "mixer" else (self.layer, self.part)
+        return self.own_key if self.part == "mixer" else (self.own_key, self.part)
 
     def for_part(self, name: str) -> "RunEntry":
         """This entry as seen by the layer's sub-part ``name`` (a block with more than one
@@ -160,13 +170,16 @@ class ModelSpec:
         for pos, entry in enumerate(self.run_order):
             if not 0 <= entry.layer < n:
                 raise ValueError(f"run_order[{pos}] names layer {entry.layer}; there are {n}")
+            if entry.instance is not None and entry.instance < 0:
+                raise ValueError(f"run_order[{pos}]: an instance's number is not negative")
             if entry.writes_cache:
-                if entry.layer in seen_writer:
+                if entry.own_key in seen_writer:
                     raise ValueError(
                         f"run_order[{pos}] runs layer {entry.layer} a second time with its own "
-                        "cache; a repeated layer must read another run's cache (cache_of)"
+                        "cache; a repeated layer must read another run's cache (cache_of) or keep "
+                        "one under a number of its own (instance)"
                     )
-                seen_writer.add(entry.layer)
+                seen_writer.add(entry.own_key)
             elif entry.cache_layer not in seen_writer:
                 raise ValueError(
                     f"run_order[{pos}] reads the cache of layer {entry.cache_layer}, "

@@ -96,9 +96,10 @@ class TokenEmbedding(Part):
     graph_safe = True
     launches_replayable = True
 
-    def __init__(self, vocab_size: int, hidden_size: int) -> None:
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0) -> None:
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
+        self.scale = float(scale)  # the token's row is multiplied by it (in float32, on its way into the stream)
         self.weight = None
 
     def param_specs(self):
@@ -106,7 +107,8 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx, position) -> torch.Tensor:
         x = ctx.workspace.get("residual", (ctx.n_tokens, self.hidden_size), torch.float32)
-        K.embed(ctx.token_ids, ctx.positions, self.weight, position.table(), x, ctx.extras.get("token_feedback"))
+        K.embed(ctx.token_ids, ctx.positions, self.weight, position.table(), x, ctx.extras.get("token_feedback"),
+                scale=self.scale)
         return x
 
 
