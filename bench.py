@@ -58,6 +58,10 @@ def parse_args():
                    help="instead of the default workload: prefill and decode of the Porovik design (biased attention, "
                         "delta-rule and gated recurrences, dense and expert feed-forwards) beside GPT-2 at equal width, "
                         "depth and vocabulary")
+    p.add_argument("--compare-fikevik", action="store_true",
+                   help="instead of the default workload: prefill and decode of the Fikevik design (attention over a window "
+                        "beside a matrix memory, linear attention with decaying keys, the norm after each gated sum) beside "
+                        "Porovik, the nearest shipped design, at equal width, depth and vocabulary, random weights")
     p.add_argument("--compare-lebedra", action="store_true",
                    help="instead of the default workload: prefill and decode of the Lebedra design (latent attention, "
                         "mixture of experts) beside GPT-2 of equal width, depth and vocabulary, at layer sizes of "
@@ -686,8 +690,9 @@ POROVIK_SIZES = {
 }
 
 
-def porovik_config(z: dict, layers: int, vocab: int, positions: int):
-    """Mixers in turn (attention, delta rule, gated recurrence); feed-forwards dense and experts in turn."""
+def porovik_config(z: dict, layers: int, vocab: int, positions: int, dense_only: bool = False):
+    """Mixers in turn (attention, delta rule, gated recurrence); feed-forwards dense and experts in turn
+    (``dense_only``: all dense)."""
     from rosellm_b200.config.porovik import PorovikConfig
 
     mixers = [
@@ -701,7 +706,7 @@ def porovik_config(z: dict, layers: int, vocab: int, positions: int):
         "architecture": "Porovik", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-5},
         "embedding": {"bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
         "layers": [{"type": mixers[i % 3][0], "mixer": mixers[i % 3][1],
-                    "mlp": moe if i % 2 else {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]})
+                    "mlp": moe if i % 2 and not dense_only else {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]})
 
 
 def compare_porovik(args):
@@ -739,6 +744,69 @@ def compare_porovik(args):
     return 0
 
 
+# Layer sizes for --compare-fikevik: width; the windowed attention's heads, key/value heads, key and value size and
+# window; heads, key and value size of the matrix memory; of the linear attention with decaying keys, and its
+# decay's rank; the feed-forwards' inner size.
+FIKEVIK_SIZES = {
+    "1024": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, window=256, m_heads=8, m_dim=64, m_vdim=128, g_heads=8,
+                 g_dim=64, g_vdim=128, g_rank=16, ff=4096),
+    "2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=256, m_heads=16, m_dim=128, m_vdim=128,
+                 g_heads=16, g_dim=128, g_vdim=128, g_rank=32, ff=8192),
+}
+
+
+def fikevik_config(z: dict, layers: int, vocab: int, positions: int):
+    """Layers in turn: attention over a window beside a matrix memory, then linear attention with decaying keys;
+    a dense gated feed-forward in each."""
+    from rosellm_b200.config.fikevik import FikevikConfig
+
+    side = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                     "mask": {"size": z["window"]}, "rot": {"dims": z["dim"], "base": 500000.0}},
+            "right": {"heads": z["m_heads"], "dim": z["m_dim"], "vdim": z["m_vdim"], "gate_cap": 15.0},
+            "left_scale": 0.6, "right_scale": 1.1}
+    gla = {"heads": z["g_heads"], "dim": z["g_dim"], "vdim": z["g_vdim"], "tau": 16.0, "decay_rank": z["g_rank"]}
+    return FikevikConfig.from_dict({
+        "architecture": "Fikevik", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-6},
+        "embedding": {"scale": 12.0}, "postln_alpha": 2.0,
+        "layers": [{"type": "gla" if i % 2 else "parallel", "mixer": gla if i % 2 else side,
+                    "mlp": {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]})
+
+
+def compare_fikevik(args):
+    """Prefill (2 x 1024 tokens) and decode (batch 8 and 64, 512 cached tokens) of Fikevik and of Porovik (the
+    nearest shipped design: attention and matrix-state recurrences in turn, here with dense feed-forwards of the
+    same inner size) at equal width, depth and vocabulary: device time by CUDA events, as the default workload."""
+    layers, vocab, positions = 6, 32000, 1024
+    clocks = Clocks()
+    clocks.start()
+    out = {"metric": "prefill and decode of Fikevik beside Porovik at equal width", "unit": "tokens/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": args.warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+           "data": "synthetic (random token ids, random weights)", "layers": layers, "vocab": vocab, "sizes": {}}
+    for name, z in FIKEVIK_SIZES.items():
+        row = {}
+        for label, cfg in (("fikevik", fikevik_config(z, layers, vocab, positions)),
+                           ("porovik", porovik_config(POROVIK_SIZES[name], layers, vocab, positions, dense_only=True))):
+            h = Harness(cfg, args.dtype, 64, graphs=not args.no_graphs)
+            try:
+                pms = h.prefill()
+                rec = {"prefill_2x1024_ms": round(pms, 4), "prefill_tok_s": round(2048 / (pms * 1e-3), 1),
+                       "weight_mb": round(h.runner.model.weight_bytes() / 1e6, 1)}
+                for b in (8, 64):
+                    ms, launches, gms, _ = h.device_decode(b, args.context, max(16, args.steps // 2), max(4, args.warmup // 2))
+                    rec[f"decode_b{b}_ms"] = round(ms, 4)
+                    rec[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    rec[f"decode_b{b}_launches"] = launches
+                    if gms is not None:
+                        rec[f"decode_b{b}_graph_ms"] = round(gms, 4)
+                row[label] = rec
+            finally:
+                h.close()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     args = parse_args()
     if args.gpus != 1:
@@ -748,6 +816,8 @@ def main():
         return compare_lebedra(args)
     if args.compare_porovik:
         return compare_porovik(args)
+    if args.compare_fikevik:
+        return compare_fikevik(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -36,6 +36,23 @@ def rotate_pairs(y: torch.Tensor, positions: torch.Tensor, dims: int, base: floa
     return out
 
 
+def window_softmax(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, temp: torch.Tensor,
+                   size: int | None) -> torch.Tensor:
+    """q [T, H, dk], k [T, G, dk], v [T, G, dv]: query i sees the keys j with 0 <= i - j < size (``None``: all
+    j <= i); query head h uses key/value head h // (H / G); score = q . k * scale * temp[h]."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    seen = (i - j >= 0) if size is None else (i - j >= 0) & (i - j < size)
+    out = torch.zeros(T, H, v.shape[-1], dtype=F64)
+    for hd in range(H):
+        g = hd // (H // G)
+        s = (q[:, hd] @ k[:, g].T) * scale * temp[hd]
+        out[:, hd] = torch.softmax(s.masked_fill(~seen, -math.inf), -1) @ v[:, g]
+    return out
+
+
 def windowed_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
     """Softmax attention over the last ``mask.size`` positions, grouped key/value heads, normed and
     rotated queries and keys, unit values, a temperature per head."""
@@ -47,31 +64,26 @@ def windowed_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) ->
     q = unit(q, eps) * w[p + "q.norm"]
     k = unit(k, eps) * w[p + "k.norm"]
     pos = torch.arange(T)
-    q = rotate_pairs(q, pos, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_pairs(k, pos, m["rot"]["dims"], m["rot"]["base"])
-    v = unit(v, eps)
-    out = torch.zeros(T, H, dv, dtype=F64)
-    size = m["mask"]["size"]
-    for hd in range(H):
-        g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].T) * m["scale"] * w[p + "temp"][hd]
-        i = torch.arange(T)[:, None]
-        j = torch.arange(T)[None, :]
-        seen = (i - j >= 0) & (i - j < size)
-        s = s.masked_fill(~seen, -math.inf)
-        out[:, hd] = torch.softmax(s, -1) @ v[:, g]
+    if m.get("rot"):
+        q = rotate_pairs(q, pos, m["rot"]["dims"], m["rot"]["base"])
+        k = rotate_pairs(k, pos, m["rot"]["dims"], m["rot"]["base"])
+    out = window_softmax(q, k, unit(v, eps), m["scale"], w[p + "temp"], m["mask"]["size"] if m.get("mask") else None)
     return out.reshape(T, H * dv) @ w[p + "o"].T
 
 
-def matrix_memory(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
-    """A matrix memory with exponential input gate and a running maximum that starts at zero."""
-    T = h.shape[0]
-    H, dk, dv, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
-    q = (h @ w[p + "q"].T).view(T, H, dk) * dk ** -0.5
-    k = (h @ w[p + "k"].T).view(T, H, dk)
-    v = (h @ w[p + "v"].T).view(T, H, dv)
-    gi = cap * torch.tanh((h @ w[p + "i"].T + w[p + "i.b"]) / cap)
-    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ w[p + "f"].T + w[p + "f.b"]) / cap))
+def capped_log_gates(zi: torch.Tensor, zf: torch.Tensor, cap: float):
+    """The logarithms of the input and forget gates from their logits: cap * tanh(z / cap), the forget gate's
+    through a log-sigmoid."""
+    return cap * torch.tanh(zi / cap), torch.nn.functional.logsigmoid(cap * torch.tanh(zf / cap))
+
+
+def memory_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gi: torch.Tensor, gf: torch.Tensor,
+                      floor: float = 1e-6) -> torch.Tensor:
+    """q, k [T, H, dk], v [T, H, dv], log gates gi, gf [T, H].  S, n and the running maximum m start at zero:
+    m_t = max(gf + m, gi); S_t = e^(gf + m - m_t) S + e^(gi - m_t) k v^T; n_t likewise with k;
+    o_t = S_t^T q / (max(|n_t . q|, e^(-m_t)) + floor)."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
     S = torch.zeros(H, dk, dv, dtype=F64)
     n = torch.zeros(H, dk, dtype=F64)
     mx = torch.zeros(H, dtype=F64)
@@ -84,26 +96,44 @@ def matrix_memory(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torc
         n = keep[:, None] * n + take[:, None] * k[t]
         mx = m_new
         num = torch.einsum("hkv,hk->hv", S, q[t])
-        den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-mx)) + 1e-6
+        den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-mx)) + floor
         out[t] = num / den[:, None]
+    return out
+
+
+def decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
+    """q, k, a [T, H, dk], v [T, H, dv]: S_t = diag(a_t) S_(t-1) + k_t v_t^T from S = 0; o_t = S_t^T q_t."""
+    T, H, dk = q.shape
+    S = torch.zeros(H, dk, v.shape[-1], dtype=F64)
+    out = torch.zeros(T, H, v.shape[-1], dtype=F64)
+    for t in range(T):
+        S = a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return out
+
+
+def matrix_memory(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
+    """A matrix memory with exponential input gate and a running maximum that starts at zero."""
+    T = h.shape[0]
+    H, dk, dv, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
+    q = (h @ w[p + "q"].T).view(T, H, dk) * dk ** -0.5
+    k = (h @ w[p + "k"].T).view(T, H, dk)
+    v = (h @ w[p + "v"].T).view(T, H, dv)
+    gi, gf = capped_log_gates(h @ w[p + "i"].T + w[p + "i.b"], h @ w[p + "f"].T + w[p + "f.b"], cap)
+    out = memory_recurrence(q, k, v, gi, gf)
     o = unit(out, eps).reshape(T, H * dv) * w[p + "norm"] * torch.sigmoid(h @ w[p + "g"].T)
     return o @ w[p + "o"].T
 
 
 def decayed_linear_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
-    """S_t = diag(a_t) S_(t-1) + k_t v_t^T with a_t = sigmoid(z_t)^(1/tau) per key channel; o_t = S_t^T q_t."""
+    """Linear attention whose state forgets per key channel: a_t = sigmoid(z_t)^(1/tau), z through a low rank."""
     T = h.shape[0]
     H, dk, dv, tau = m["heads"], m["dim"], m["vdim"], float(m["tau"])
     q = (h @ w[p + "q"].T).view(T, H, dk) * dk ** -0.5
     k = (h @ w[p + "k"].T).view(T, H, dk)
     v = (h @ w[p + "v"].T).view(T, H, dv)
     z = ((h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "a2.b"]).view(T, H, dk)
-    a = torch.sigmoid(z) ** (1.0 / tau)
-    S = torch.zeros(H, dk, dv, dtype=F64)
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for t in range(T):
-        S = a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    out = decay_recurrence(q, k, v, torch.sigmoid(z) ** (1.0 / tau))
     o = (unit(out, eps) * w[p + "norm"]).reshape(T, H * dv)
     g = h @ w[p + "g"].T
     return (o * g * torch.sigmoid(g)) @ w[p + "o"].T
@@ -130,8 +160,10 @@ MIXERS = {"gla": decayed_linear_attention, "parallel": side_by_side}
 
 
 def layer(x: torch.Tensor, w: dict, cfg: dict, i: int) -> torch.Tensor:
-    lc = cfg["layers"][i]
-    p = f"l{lc.get('weights_of', i)}."
+    lc, owner = cfg["layers"][i], i
+    while cfg["layers"][owner].get("weights_of") is not None:  # a layer that runs another layer's tensors
+        owner = cfg["layers"][owner]["weights_of"]
+    p = f"l{owner}."
     eps, alpha = cfg["norm"]["eps"], cfg["postln_alpha"]
     y = MIXERS[lc["type"]](x, w, p + "mix.", lc["mixer"], eps)
     x = sublayer_join(x, y, w, p + "rg1", p + "norm1", alpha, eps)
