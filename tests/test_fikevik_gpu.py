@@ -372,20 +372,45 @@ def folders(tmp_path_factory):
 _plain: dict = {}
 
 
-def plain_logits(folder, toks):
-    key = (folder, tuple(toks))
+def plain_logits(folder, toks, how="exact"):
+    """``exact``: float64.  ``float32``: the same functions on float32 tensors.  ``bfloat16``: float64 with the
+    activations rounded to bfloat16 where a 16-bit engine stores them.  The last two show how far rounding alone
+    moves the logits of this very sequence, which is what the tolerances below are tied to."""
+    key = (folder, tuple(toks), how)
     if key not in _plain:
         if folder not in _plain:
-            _plain[folder] = load_folder(folder)
-        cfg, w = _plain[folder]
-        _plain[key] = P.forward(cfg, w, toks)
+            cfg, w = load_folder(folder)
+            _plain[folder] = (cfg, w, {k: v.float() for k, v in w.items()})
+        cfg, w, w32 = _plain[folder]
+        if how == "float32":
+            _plain[key] = P.forward(cfg, w32, toks).double()
+        else:
+            _plain[key] = P.forward(cfg, w, toks, rounding=P.to_bfloat16_and_back if how == "bfloat16" else None)
     return _plain[key]
 
 
+def centred_rms(d):
+    d = d - d.mean()
+    return float(d.pow(2).mean().sqrt())
+
+
+def row_limit(folder, toks, pos, dtype):
+    """float32: 3e-4 on a logit, or five times what float32 rounding moves this row in the plain implementation.
+    bfloat16: the row's error (mean taken off, root mean square over the vocabulary, over that of the plain row)
+    0.12, or three times what bfloat16 storage moves this row.  The second figures matter where the model itself
+    magnifies rounding: a matrix memory whose state one token dominates, read by a query nearly at right angles to
+    that token's key, has an output whose direction the remaining small terms decide, and the heads' norm
+    scales it up to full size."""
+    ref = plain_logits(folder, toks)[pos]
+    if dtype == "float32":
+        return max(3e-4, 5.0 * float((plain_logits(folder, toks, "float32")[pos] - ref).abs().max()))
+    return max(0.12, 3.0 * centred_rms(plain_logits(folder, toks, "bfloat16")[pos] - ref) / centred_rms(ref))
+
+
 def check(folder, reqs, trace, got, dtype):
-    """float32: every wanted row within 3e-4 of the plain logits.  bfloat16: the row's error (mean taken off, root
-    mean square over the vocabulary, over that of the plain row) below 0.12 for all but 3 % of the rows."""
-    over, total, errs = 0, 0, []
+    """Every wanted row within ``row_limit`` of the plain logits: in float32 all rows, in bfloat16 all but 3 %;
+    and no more than a tenth of the rows may owe their limit to the model's own magnification."""
+    over, total, lifted, errs = 0, 0, 0, []
     for s, want in zip(trace.steps, trace.wanted):
         if not want:
             continue
@@ -394,17 +419,18 @@ def check(folder, reqs, trace, got, dtype):
             ref = plain_logits(folder, reqs[rid])[pos]
             assert torch.isfinite(arr[row]).all()
             total += 1
+            limit = row_limit(folder, reqs[rid], pos, dtype)
+            lifted += limit > (3e-4 if dtype == "float32" else 0.12)
             if dtype == "float32":
                 diff = float((arr[row] - ref).abs().max())
-                assert diff <= 3e-4, (f"step {s['step']}: request {rid} position {pos}: |logits - plain| = {diff:.3e}; "
-                                      f"entries {[(e['id'], len(e['tokens'])) for e in s['entries']]}")
+                assert diff <= limit, (f"step {s['step']}: request {rid} position {pos}: |logits - plain| = {diff:.3e} > "
+                                       f"{limit:.1e}; entries {[(e['id'], len(e['tokens'])) for e in s['entries']]}")
             else:
-                d = arr[row] - ref
-                d = d - d.mean()
-                errs.append(float(d.pow(2).mean().sqrt() / (ref - ref.mean()).pow(2).mean().sqrt()))
-                over += errs[-1] > 0.12
+                errs.append(centred_rms(arr[row] - ref) / centred_rms(ref))
+                over += errs[-1] > limit
     assert over <= 0.03 * total + 1, (f"{over} of {total} rows differ from the plain logits beyond bfloat16 rounding; "
                                       f"quantiles 50/90/99 %: {np.quantile(errs, [0.5, 0.9, 0.99])}")
+    assert lifted <= 0.1 * total + 2, f"{lifted} of {total} rows are judged by the model's magnification of rounding"
 
 
 def requests_for(name, lens, seed):
@@ -552,6 +578,6 @@ def test_greedy_generation_through_the_entry_point(folders, name, dtype):
         for tok in out:
             ref = plain_logits(folders[name], ids)[-1]
             gap = float(ref.max() - ref[tok])
-            spread = float((ref - ref.mean()).pow(2).mean().sqrt())
-            assert gap <= (3e-4 if dtype == "float32" else 0.16 * spread), (gap, spread)
+            limit = row_limit(folders[name], ids, len(ids) - 1, dtype)  # on a logit, or on the row's relative error
+            assert gap <= (2 * limit if dtype == "float32" else 1.4 * limit * centred_rms(ref)), (gap, limit)
             ids.append(tok)

@@ -61,7 +61,7 @@ def model(vocab, width, eps, emb_scale, alpha, layers):
             "postln_alpha": alpha, "layers": out}
 
 
-RAW_A = model(131, 64, 1e-5, 3.0, 1.5, [
+RAW_A = model(131, 64, 1e-5, 3.0, 2.25, [
     (gla(3, 24, 10, 4.0, 5), dense(100)),
     (side(left(6, 2, 20, 12, 0.3, 7, (12, 10000.0)), right(3, 8, 20, 5.0), 0.7, 1.3), None),
     (again(0), None),
