@@ -128,15 +128,17 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __r
   if (i < n) out[i] = __float2bfloat16_rn(x[i]);
 }
 
-// stream[i] = rmsnorm(alpha * stream[i] + sigmoid(z[i]) * (s0 * y0[i] + s1 * y1[i])) * gamma: the norm AFTER the sum
+// stream[i] = rmsnorm(alpha * stream[i] + sigmoid(z[i] + zb) * (s0 * y0[i] + s1 * y1[i])) * gamma: the norm AFTER the sum
 // of a layer that normalises the stream itself, with the sublayer's result (of one mixer, or of two side by
-// side with a weight each) passing a gate whose logits z the caller computed from the sublayer's input.  The new
+// side with a weight each) passing a gate whose logits z the caller computed from the sublayer's input (zb: the
+// logits' bias, one entry a column, where the product that made z did not add it; null: none).  The new
 // row also goes out in bfloat16 (copy) for the products of the next sublayer.  The row is kept in shared memory
 // between the statistic and the scaling where it fits (KEEP), else worked out a second time.
 template <bool KEEP>
 __global__ __launch_bounds__(256) void gated_join_norm_kernel(const float* __restrict__ y0, long ld0, float s0,
                                                               const float* __restrict__ y1, long ld1, float s1,
                                                               const float* __restrict__ z, long ldz,
+                                                              const float* __restrict__ zb,
                                                               const float* __restrict__ gamma, float* __restrict__ stream,
                                                               long lds, __nv_bfloat16* __restrict__ copy, long ldc,
                                                               int n_rows, int width, float eps, float alpha) {
@@ -152,7 +154,7 @@ __global__ __launch_bounds__(256) void gated_join_norm_kernel(const float* __res
   auto joined = [&](int d) {
     float y = s0 * a[d];
     if (b != nullptr) y = fmaf(s1, b[d], y);
-    const float g = zr != nullptr ? 1.0f / (1.0f + expf(-zr[d])) : 1.0f;
+    const float g = zr != nullptr ? 1.0f / (1.0f + expf(-(zr[d] + (zb != nullptr ? zb[d] : 0.f)))) : 1.0f;
     return fmaf(alpha, xr[d], g * y);
   };
   float ss = 0.f;
@@ -231,10 +233,10 @@ RL_EXPORT int rl_rmsnorm_add_norm(int out_dtype, const float* y, long ldy, const
   return 0;
 }
 
-// stream = rmsnorm(alpha * stream + sigmoid(z) * (s0 * y0 + s1 * y1)) * gamma (y1 may be null; z null: no gate), with an optional
+// stream = rmsnorm(alpha * stream + sigmoid(z + zb) * (s0 * y0 + s1 * y1)) * gamma (y1 may be null; z null: no gate; zb null: no bias), with an optional
 // bfloat16 copy of the new rows; see the kernel.
 RL_EXPORT int rl_gated_join_norm(const float* y0, long ld0, float s0, const float* y1, long ld1, float s1, const float* z,
-                                 long ldz, const float* gamma, float* stream_rows, long lds, void* copy, long ldc,
+                                 long ldz, const float* zb, const float* gamma, float* stream_rows, long lds, void* copy, long ldc,
                                  int n_rows, int width, float eps, float alpha, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (width <= 0 || y0 == nullptr) return -2;
@@ -242,9 +244,9 @@ RL_EXPORT int rl_gated_join_norm(const float* y0, long ld0, float s0, const floa
   const size_t row_bytes = (size_t)width * sizeof(float);
   if (row_bytes <= 40 * 1024)
     rl::launch_pdl(rl::gated_join_norm_kernel<true>, n_rows, threads, row_bytes, stream, y0, ld0, s0, y1, ld1, s1, z, ldz,
-                   gamma, stream_rows, lds, (__nv_bfloat16*)copy, ldc, n_rows, width, eps, alpha);
+                   zb, gamma, stream_rows, lds, (__nv_bfloat16*)copy, ldc, n_rows, width, eps, alpha);
   else
-    rl::launch_pdl(rl::gated_join_norm_kernel<false>, n_rows, threads, 0, stream, y0, ld0, s0, y1, ld1, s1, z, ldz, gamma,
+    rl::launch_pdl(rl::gated_join_norm_kernel<false>, n_rows, threads, 0, stream, y0, ld0, s0, y1, ld1, s1, z, ldz, zb, gamma,
                    stream_rows, lds, (__nv_bfloat16*)copy, ldc, n_rows, width, eps, alpha);
   RL_CHECK_LAUNCH();
   return 0;

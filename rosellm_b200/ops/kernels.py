@@ -176,7 +176,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
                                           F, F, I, P, P, I, P, P, I, I, P, P]
         lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, F, P]
-        lib.rl_gated_join_norm.argtypes = [P, L, F, P, L, F, P, L, P, P, L, P, L, I, I, F, F, P]
+        lib.rl_gated_join_norm.argtypes = [P, L, F, P, L, F, P, L, P, P, P, L, P, L, I, I, F, F, P]
         lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
@@ -1425,9 +1425,11 @@ def qkv_norm_rotate(q, k, v, positions, *, n_heads: int, n_kv: int, dk: int, dv:
     _ok(rc, "qkv_norm_rotate")
 
 
-def gated_join_norm(y0, s0: float, y1, s1: float, z, gamma, eps: float, alpha: float, stream_rows, copy=None) -> None:
-    """stream = rmsnorm(alpha * stream + sigmoid(z) * (s0 * y0 + s1 * y1)) * gamma, row by row in float32 (``y1`` may be
-    ``None``; ``z`` ``None``: no gate); ``copy`` (bfloat16, or ``None``) receives the new rows rounded."""
+def gated_join_norm(y0, s0: float, y1, s1: float, z, gamma, eps: float, alpha: float, stream_rows, copy=None,
+                    z_bias=None) -> None:
+    """stream = rmsnorm(alpha * stream + sigmoid(z + z_bias) * (s0 * y0 + s1 * y1)) * gamma, row by row in float32
+    (``y1`` may be ``None``; ``z`` ``None``: no gate; ``z_bias`` float32 [width] or ``None``); ``copy`` (bfloat16, or
+    ``None``) receives the new rows rounded."""
     n, width = stream_rows.shape
     _need(stream_rows, "stream_rows", torch.float32)
     _need(gamma, "gamma", torch.float32)
@@ -1439,11 +1441,15 @@ def gated_join_norm(y0, s0: float, y1, s1: float, z, gamma, eps: float, alpha: f
             raise KernelError(f"gated_join_norm: {name} has another shape")
     if gamma.numel() != width:
         raise KernelError("gated_join_norm: the norm's weight has another size")
+    if z_bias is not None:
+        _need(z_bias, "z_bias", torch.float32)
+        if z_bias.numel() != width or z is None:
+            raise KernelError("gated_join_norm: the gate's bias has one entry a column, and needs the gate's logits")
     if copy is not None:
         _need(copy, "copy", torch.bfloat16)
         if tuple(copy.shape) != (n, width):
             raise KernelError("gated_join_norm: the copy has another shape")
     rc = _lib().rl_gated_join_norm(_ptr(y0), y0.stride(0), float(s0), _ptr(y1), 0 if y1 is None else y1.stride(0), float(s1),
-                                   _ptr(z), 0 if z is None else z.stride(0), _ptr(gamma), _ptr(stream_rows), stream_rows.stride(0), _ptr(copy),
+                                   _ptr(z), 0 if z is None else z.stride(0), _ptr(z_bias), _ptr(gamma), _ptr(stream_rows), stream_rows.stride(0), _ptr(copy),
                                    0 if copy is None else copy.stride(0), n, width, float(eps), float(alpha), _stream())
     _ok(rc, "gated_join_norm")

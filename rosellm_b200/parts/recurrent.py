@@ -37,7 +37,11 @@ class _StateMixer(Part):
     graph_safe = True
     launches_replayable = True
 
-    def _project(self, ctx, h):
+    def _project(self, ctx, h, proj=None):
+        """The packed projections of the layer's input, float32 [tokens, rows of ``proj_weight``]: computed here,
+        or (``proj``) handed in by a block that multiplies several parts' packed weights in one product."""
+        if proj is not None:
+            return proj
         proj = ctx.workspace.get("mixer_proj", (ctx.n_tokens, self.proj_weight.shape[0]), torch.float32)
         K.linear(h, self.proj_weight, None, proj)
         return proj
@@ -176,6 +180,8 @@ class DecayedLinearAttention(_StateMixer):
     ``silu(W_g h)``, then ``W_o``.  ``low_rank``: the inner size of the decay's projection; ``None`` takes it
     from the bound tensors.  The decay is evaluated as ``exp(logsigmoid(z) / tau)`` in float32."""
 
+    takes_projection = True  # forward(.., proj=): the input times ``proj_weight``, made by the caller
+
     def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, tau: float, norm_eps: float,
                  low_rank: int | None = None, query_scale: float | None = None) -> None:
         if key_dim > 256 or value_dim > 256:
@@ -212,8 +218,8 @@ class DecayedLinearAttention(_StateMixer):
         self.a_bias, self.out_norm, self.out_weight = t["a_bias"], t["out_norm"], t["out_weight"]
         self._pad_out_weight()
 
-    def forward(self, ctx, run, h, x, add: bool = True) -> None:
-        proj = self._project(ctx, h)
+    def forward(self, ctx, run, h, x, add: bool = True, proj=None) -> None:
+        proj = self._project(ctx, h, proj)
         buf, view = self._out_buffer(ctx)
         mode = K.RECURRENCES["decayed_keys"]
         prep, oraw = self._scratch(ctx, mode, self.key_dim, self.value_dim)
@@ -239,6 +245,8 @@ class MatrixMemory(_StateMixer):
 
     The state slot holds, per head, the matrix with the normaliser as one more column ([key_dim, value_dim +
     1]: n obeys S's recurrence with a value of 1), and behind all matrices the heads' running maxima."""
+
+    takes_projection = True  # forward(.., proj=): the input times ``proj_weight``, made by the caller
 
     def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, gate_cap: float, norm_eps: float,
                  floor_eps: float = 1e-6, query_scale: float | None = None) -> None:
@@ -270,8 +278,8 @@ class MatrixMemory(_StateMixer):
         self.i_bias, self.f_bias, self.out_norm, self.out_weight = t["i_bias"], t["f_bias"], t["out_norm"], t["out_weight"]
         self._pad_out_weight()
 
-    def forward(self, ctx, run, h, x, add: bool = True) -> None:
-        proj = self._project(ctx, h)
+    def forward(self, ctx, run, h, x, add: bool = True, proj=None) -> None:
+        proj = self._project(ctx, h, proj)
         buf, view = self._out_buffer(ctx)
         mode = K.RECURRENCES["matrix_memory"]
         prep, oraw = self._scratch(ctx, mode, self.key_dim, self.value_dim + 1)

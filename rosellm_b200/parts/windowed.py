@@ -32,6 +32,8 @@ class WindowAttention(BiasedAttention):
     heads through ``W_o``.  The cache gives pages back once the window has passed them.  Norms, angles,
     rotation, scores, softmax and the weighted sums are float32 in both precisions."""
 
+    takes_projection = True  # forward(.., proj=): the input times ``proj_weight``, made by the caller
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, scale: float,
                  norm_eps: float, window: int | None = None, rot_dims: int = 0, rot_base: float = 10000.0,
                  qk_norm: bool = True, unit_values: bool = True, head_temperature: bool = True) -> None:
@@ -75,10 +77,11 @@ class WindowAttention(BiasedAttention):
         self.q_norm, self.k_norm, self.head_temp = t.get("q_norm"), t.get("k_norm"), t.get("head_temp")
         self.slopes = self.mix_weight = None
 
-    def forward(self, ctx, run, h, x, add: bool = True) -> None:
+    def forward(self, ctx, run, h, x, add: bool = True, proj=None) -> None:
         n, ws = ctx.n_tokens, ctx.workspace
-        proj = ws.get("mixer_proj", (n, self.proj_weight.shape[0]), torch.float32)
-        K.linear(h, self.proj_weight, None, proj)
+        if proj is None:  # else: a block has multiplied this part's packed weight together with others'
+            proj = ws.get("mixer_proj", (n, self.proj_weight.shape[0]), torch.float32)
+            K.linear(h, self.proj_weight, None, proj)
         o = self.offsets
         q = proj[:, o["q"]:o["q"] + self.q_width]
         k = proj[:, o["k"]:o["k"] + self.k_width]
