@@ -761,13 +761,13 @@ def fikevik_config(z: dict, layers: int, vocab: int, positions: int):
     from rosellm_b200.config.fikevik import FikevikConfig
 
     side = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
-                     "mask": {"size": z["window"]}, "rot": {"dims": z["dim"], "base": 500000.0}},
+                     "mask": {"size": z["window"]}, "rot": {"dims": z["dim"], "base": 10000.0}},
             "right": {"heads": z["m_heads"], "dim": z["m_dim"], "vdim": z["m_vdim"], "gate_cap": 15.0},
-            "left_scale": 0.6, "right_scale": 1.1}
-    gla = {"heads": z["g_heads"], "dim": z["g_dim"], "vdim": z["g_vdim"], "tau": 16.0, "decay_rank": z["g_rank"]}
+            "left_scale": 0.75, "right_scale": 1.25}
+    gla = {"heads": z["g_heads"], "dim": z["g_dim"], "vdim": z["g_vdim"], "tau": 8.0, "decay_rank": z["g_rank"]}
     return FikevikConfig.from_dict({
-        "architecture": "Fikevik", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-6},
-        "embedding": {"scale": 12.0}, "postln_alpha": 2.0,
+        "architecture": "Fikevik", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-5},
+        "embedding": {"scale": float(z["width"]) ** 0.5}, "postln_alpha": 1.5,
         "layers": [{"type": "gla" if i % 2 else "parallel", "mixer": gla if i % 2 else side,
                     "mlp": {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]})
 

@@ -495,7 +495,8 @@ RL_EXPORT int rl_bias_kv_store(int cache_dtype, const float* k, long ldk, const 
 namespace rl {
 
 // What a layer does to its queries, keys and values between the projections and the cache, in place on the
-// float32 columns of the packed projections, a warp a (token, head):
+// float32 columns of the packed projections, a warp a (token, head); a token's heads are spread over the blocks
+// of grid row y, so that a step of few tokens is as many short chains side by side, not one long one:
 //   queries and keys: each head's entries divided by their root mean square (eps inside the root) and
 //     multiplied by a weight the heads share (q_norm / k_norm; absent: left as they are), then the first
 //     `rot_dims` entries turned, entry 2i with entry 2i + 1, by the angle position * freq[i];
@@ -515,7 +516,11 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const float pos = (float)positions[tok];
   const int units = n_heads + n_kv + (unit_values ? n_kv : 0);
-  for (int u = warp; u < units; u += n_warps) {
+  // the token's angles are the same for all its heads: their sines and cosines once a block
+  __shared__ float2 turn[128];
+  for (int i = threadIdx.x; 2 * i < rot_dims; i += blockDim.x) sincosf(pos * freq[i], &turn[i].y, &turn[i].x);
+  __syncthreads();
+  for (int u = blockIdx.y * n_warps + warp; u < units; u += n_warps * gridDim.y) {
     if (u < n_heads + n_kv) {
       const bool is_q = u < n_heads;
       float* e = is_q ? q + (size_t)tok * ldq + (size_t)u * dk : k + (size_t)tok * ldk + (size_t)(u - n_heads) * dk;
@@ -534,8 +539,7 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
           if (d1 < dk) b *= w[d1];
         }
         if (d1 < rot_dims) {
-          float sn, cs;
-          sincosf(pos * freq[i], &sn, &cs);
+          const float cs = turn[i].x, sn = turn[i].y;
           const float ra = a * cs - b * sn, rb = b * cs + a * sn;
           a = ra;
           b = rb;
@@ -563,10 +567,14 @@ RL_EXPORT int rl_qkv_norm_rotate(float* q, long ldq, float* k, long ldk, float* 
                                  int n_kv, int dk, int dv, int rot_dims, int unit_values, float eps, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || dk <= 0 || dv <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > dk ||
-      (rot_dims > 0 && freq == nullptr) || (q_norm == nullptr) != (k_norm == nullptr))
+      rot_dims > 256 || (rot_dims > 0 && freq == nullptr) || (q_norm == nullptr) != (k_norm == nullptr))
     return -2;
-  rl::launch_pdl(rl::qkv_norm_rotate_kernel, n_tokens, 128, 0, stream, q, ldq, k, ldk, v, ldv, q_norm, k_norm, freq,
-                 positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, eps);
+  const int units = n_heads + n_kv + (unit_values ? n_kv : 0);
+  // a warp a (token, head) in a step of few tokens; with many tokens a block takes more of a token's heads
+  const int want = (148 * 40 + n_tokens - 1) / n_tokens, most = units < 4 * 1024 ? (units + 3) / 4 : 1024;
+  const int rows = want < most ? want : most;
+  rl::launch_pdl(rl::qkv_norm_rotate_kernel, dim3(n_tokens, rows), 128, 0, stream, q, ldq, k, ldk, v, ldv, q_norm, k_norm,
+                 freq, positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, eps);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -19,8 +19,8 @@
 //     The normaliser n_t = w n_(t-1) + k is one more column of the state, whose value is 1 for every token, so
 //     the state has dv = (value size + 1) columns and n . r arrives as the output's last column.  Output:
 //     o / (max(|n . r|, exp(-m_t)) + floor_eps), each head's divided by its root mean square, times a weight
-//     per (head, column), times sigmoid(g).  `recurrence_gate_scan_kernel`, a warp a (request, head), walks the
-//     tokens in their order for m_t and leaves (w, exp(i - m_t), exp(-m_t)) per (token, head).
+//     per (head, column), times sigmoid(g).  `recurrence_gate_scan_kernel` walks a request's tokens in their order for
+//     m_t, a warp a (request, head), and leaves (w, exp(i - m_t), exp(-m_t)) per (token, head).
 //
 // The inputs are columns of one float32 matrix (the packed projections of the layer's input).  Three kernels:
 //   `recurrence_prep_kernel`, a block a token: everything that does not depend on the state (sigmoids,
@@ -63,47 +63,89 @@ struct RecurParams {
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// The running maximum of the matrix memory and what follows from it, token by token in order (so that the
-// numbers do not depend on how a prompt was cut): a warp a (request, head), 32 tokens' gates worked out at
-// once, then walked in turn.
-__global__ __launch_bounds__(128) void recurrence_gate_scan_kernel(const RecurParams p) {
+// The running maximum of the matrix memory and what follows from it.  The maximum is walked token by token in
+// order (so that the numbers do not depend on how a prompt was cut), a warp a (request, head); what does not lie
+// on that chain is spread over the block's threads: a block takes a request and SCAN_HEADS heads and works through
+// the request's tokens in rounds of SCAN_TOKENS: (a) the capped gates of all the round's (token, head) pairs
+// into shared memory, (b) each warp walks its head's tokens, a token costing the chain one sum and one maximum,
+// and parks the maximum before and after every token, (c) the exponentials of all pairs.
+// 16 warps a block: the gates' functions are a few hundred dependent instructions a (token, head), which four warps
+// alone on an SM would run at one instruction every few cycles
+constexpr int SCAN_TOKENS = 512, SCAN_THREADS = 512, SCAN_HEADS = 1, SCAN_ROW = SCAN_TOKENS + 8;  // rows apart by 8 banks
+
+__global__ __launch_bounds__(SCAN_THREADS) void recurrence_gate_scan_kernel(const RecurParams p) {
+  __shared__ float s_i[SCAN_HEADS * SCAN_ROW], s_f[SCAN_HEADS * SCAN_ROW], s_before[SCAN_HEADS * SCAN_ROW], s_after[SCAN_HEADS * SCAN_ROW];
   pdl_begin();
-  const int req = blockIdx.x, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (head >= p.n_heads) return;
+  const int req = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h0 = blockIdx.y * SCAN_HEADS, nh = min(SCAN_HEADS, p.n_heads - h0);
+  if (nh <= 0) return;
   const int slot = p.slots[req];
   if (slot < 0) return;
   const int t0 = p.q_start[req], t1 = p.q_start[req + 1];
-  float* mp = p.state + (size_t)slot * p.state_stride + p.m_off + head;
-  float m = *mp;
-  const float bi = p.a_bias[head], bf = p.w0[head];
-  for (int base = t0; base < t1; base += 32) {
-    const int t = base + lane;
-    float gi = 0.f, gf = 0.f;
-    if (t < t1) {
-      const float* row = p.proj + (size_t)t * p.ldp;
-      gi = p.cap * tanhf((row[p.off_a + head] + bi) / p.cap);
-      gf = logsigmoidf_(p.cap * tanhf((row[p.off_w + head] + bf) / p.cap));
-    }
-    float m_before = 0.f, m_after = 0.f;
-    const int n = min(32, t1 - base);
-    for (int j = 0; j < n; ++j) {
-      const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
-      const float m_new = fmaxf(fj + m, ij);
-      if (lane == j) {
-        m_before = m;
-        m_after = m_new;
+  float* mp = p.state + (size_t)slot * p.state_stride + p.m_off + h0 + warp;
+  float m = warp < nh ? *mp : 0.f;
+  for (int base = t0; base < t1; base += SCAN_TOKENS) {
+    const int n = min(SCAN_TOKENS, t1 - base);
+    // (a) all of a thread's logits are on their way before the first is used
+    float zi[SCAN_TOKENS * SCAN_HEADS / SCAN_THREADS], zf[SCAN_TOKENS * SCAN_HEADS / SCAN_THREADS];
+#pragma unroll
+    for (int k = 0; k < SCAN_TOKENS * SCAN_HEADS / SCAN_THREADS; ++k) {
+      const int idx = threadIdx.x + k * SCAN_THREADS, tt = idx / nh, hh = idx - tt * nh;
+      if (idx < n * nh) {
+        const float* row = p.proj + (size_t)(base + tt) * p.ldp;
+        zi[k] = row[p.off_a + h0 + hh] + p.a_bias[h0 + hh];
+        zf[k] = row[p.off_w + h0 + hh] + p.w0[h0 + hh];
       }
-      m = m_new;
     }
-    if (t < t1) {
-      float* g = p.gates + ((size_t)t * p.n_heads + head) * 4;
-      g[0] = expf(gf + m_before - m_after);
-      g[1] = expf(gi - m_after);
+#pragma unroll
+    for (int k = 0; k < SCAN_TOKENS * SCAN_HEADS / SCAN_THREADS; ++k) {
+      const int idx = threadIdx.x + k * SCAN_THREADS, tt = idx / nh, hh = idx - tt * nh;
+      if (idx < n * nh) {
+        s_i[hh * SCAN_ROW + tt] = p.cap * tanhf(zi[k] / p.cap);
+        s_f[hh * SCAN_ROW + tt] = logsigmoidf_(p.cap * tanhf(zf[k] / p.cap));
+      }
+    }
+    __syncthreads();
+    // (b) every lane of the head's warp walks the same chain, eight tokens at a time: their gates are taken from
+    // shared memory into registers first (loads that do not wait for m; past the round's last token gates that
+    // leave m as it is), and the maxima are parked by lane 0 after the eight steps, so nothing but one sum and
+    // one maximum a token lies between a token's m and the next
+    if (warp < nh) {
+      const float* gi = s_i + warp * SCAN_ROW;
+      const float* gf = s_f + warp * SCAN_ROW;
+      for (int t8 = 0; t8 < n; t8 += 8) {
+        float f8[8], i8[8], m8[9];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          f8[k] = t8 + k < n ? gf[t8 + k] : 0.f;
+          i8[k] = t8 + k < n ? gi[t8 + k] : -INFINITY;
+        }
+        m8[0] = m;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) m8[k + 1] = fmaxf(f8[k] + m8[k], i8[k]);
+        m = m8[8];
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (t8 + k < n) {
+              s_before[warp * SCAN_ROW + t8 + k] = m8[k];
+              s_after[warp * SCAN_ROW + t8 + k] = m8[k + 1];
+            }
+        }
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * nh; idx += blockDim.x) {
+      const int tt = idx / nh, hh = idx - tt * nh, at = hh * SCAN_ROW + tt;
+      const float m_after = s_after[at];
+      float* g = p.gates + ((size_t)(base + tt) * p.n_heads + h0 + hh) * 4;
+      g[0] = expf(s_f[at] + s_before[at] - m_after);
+      g[1] = expf(s_i[at] - m_after);
       g[2] = expf(-m_after);
     }
+    __syncthreads();  // the next round overwrites what this one read
   }
-  if (lane == 0) *mp = m;
+  if (warp < nh && lane == 0) *mp = m;
 }
 
 // A block takes one token and `heads_per_block` heads.  Dynamic shared memory (MODE 0): tanh of the low-rank
@@ -496,7 +538,7 @@ RL_EXPORT int rl_recurrence(int mode, int out_dtype, const float* proj, long ldp
     if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<2, float>, n_tokens, 256, 0, stream, p);
     else rl::launch_pdl(rl::recurrence_out_kernel<2, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
   } else {
-    rl::launch_pdl(rl::recurrence_gate_scan_kernel, dim3(n_reqs, (n_heads + 3) / 4), 128, 0, stream, p);
+    rl::launch_pdl(rl::recurrence_gate_scan_kernel, dim3(n_reqs, (n_heads + rl::SCAN_HEADS - 1) / rl::SCAN_HEADS), rl::SCAN_THREADS, 0, stream, p);
     rl::launch_pdl(rl::recurrence_prep_kernel<3>, prep_grid, 256, 0, stream, p, hpb);
     rl::dispatch_seq<1>(p, n_reqs, stream);
     if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<3, float>, n_tokens, 256, 0, stream, p);

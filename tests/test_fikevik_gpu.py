@@ -1,6 +1,7 @@
 """Fikevik on the GPU: every mechanism's kernels against the plain implementation's function for it, then
 whole models through the engine's step function, cache and state slots, scheduler and entry point."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -581,3 +582,35 @@ def test_greedy_generation_through_the_entry_point(folders, name, dtype):
             limit = row_limit(folders[name], ids, len(ids) - 1, dtype)  # on a logit, or on the row's relative error
             assert gap <= (2 * limit if dtype == "float32" else 1.4 * limit * centred_rms(ref)), (gap, limit)
             ids.append(tok)
+
+
+@pytest.mark.parametrize("stream", [False, True], ids=["whole", "stream"])
+def test_the_command_line_generates_the_plain_greedy_tokens(folders, stream):
+    """``python -m rosellm_b200.cli_generate`` as a child process, in 32 bits, on a model whose layers run other
+    layers' tensors: the ids it prints are the plain arg-max, token after token."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompt = np.random.default_rng(12).integers(0, TINY["B"]["raw"]["vocab"], 23).tolist()
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    res = subprocess.run([sys.executable, "-m", "rosellm_b200.cli_generate", "--model", folders["B"], "--prompt-ids",
+                          ",".join(map(str, prompt)), "--max-new-tokens", "6", "--no-stop-on-eos", "--dtype", "fp32",
+                          "--max-num-batched-tokens", "64", "--max-num-seqs", "2", "--page-size", str(TINY["B"]["page_size"]),
+                          "--kv-cache-max-tokens", "256", *(["--stream"] if stream else [])],
+                         capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert res.returncode == 0, res.stderr[-3000:]
+    if stream:
+        line = next(l for l in res.stdout.splitlines() if l.startswith("[rosellm_b200] streaming output: "))
+        got = [int(t) for t in line.split(": ", 1)[1].split()]
+    else:
+        import ast
+
+        line = next(l for l in res.stdout.splitlines() if l.startswith("[rosellm_b200] output: "))
+        got = list(ast.literal_eval(line.split(": ", 1)[1]))
+    assert len(got) == 6
+    ids = list(prompt)
+    for tok in got:
+        ref = plain_logits(folders["B"], ids)[-1]
+        assert float(ref.max() - ref[tok]) <= 2 * row_limit(folders["B"], ids, len(ids) - 1, "float32")
+        ids.append(tok)

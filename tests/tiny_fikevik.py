@@ -82,7 +82,7 @@ RAW_C = model(77, 48, 1e-4, 0.5, 3.0, [
     (side(left(3, 3, 16, 24, 0.25, None, (16, 1.0e6)), right(2, 16, 16, 4.0), 0.5, 2.0), dense(16)),
 ])
 RAW_D = model(2000, 384, 1e-5, 20.0, 2.5, [
-    (side(left(12, 4, 48, 80, 0.14, 100, (32, 500000.0)), right(6, 32, 96, 15.0), 0.8, 1.2), dense(640)),
+    (side(left(12, 4, 48, 80, 0.14, 100, (32, 300000.0)), right(6, 32, 96, 15.0), 0.8, 1.2), dense(640)),
     (gla(6, 64, 96, 16.0, 24), dense(512)),
     (again(0), None),
     (gla(3, 96, 136, 32.0, 8), None),
@@ -109,9 +109,9 @@ TINY = {
     "F": dict(raw=RAW_F, seed=46, std=0.2, page_size=8),
 }
 # A wide one: the products' tensor-core paths, windows of many key tiles, states of 64 and 128 columns.
-RAW_WIDE = model(3000, 1024, 1e-5, 30.0, 2.0, [
-    (side(left(16, 4, 64, 64, 0.125, 300, (64, 500000.0)), right(8, 64, 128, 15.0), 0.6, 1.1), dense(2048)),
-    (gla(8, 64, 128, 16.0, 16), dense(2048)),
+RAW_WIDE = model(3000, 1024, 1e-5, 30.0, 1.75, [
+    (side(left(16, 4, 64, 64, 0.125, 300, (64, 250000.0)), right(8, 64, 128, 15.0), 0.8, 1.25), dense(2048)),
+    (gla(8, 64, 128, 12.0, 16), dense(2048)),
     (again(0), None),
     (again(1), None),
 ])
