@@ -354,6 +354,15 @@ def test_the_memorys_running_maximum_over_a_long_sequence(cuts):
                            gate_spread=spread) < 1e-4, (cap, spread)
 
 
+@pytest.mark.parametrize("cuts", [(2000,), (511, 2, 513), (512,), (1024, 1)])
+def test_the_memorys_gates_over_the_kernels_rounds_of_tokens(cuts):
+    """The kernel of the running maximum takes a request's tokens in rounds of 512: portions longer than a round,
+    and portions that end a token before a round's end, on it and a token after it; three requests a step."""
+    assert _state_case("matrix_memory", "float32", 3, 16, 24, [1100, 513, 512], cuts, seed=3, cap=6.0,
+                       gate_spread=3.0) < 1e-4, cuts
+    assert _state_case("decayed_keys", "float32", 2, 16, 24, [1100, 513], cuts, seed=4, tau=8.0, rank=5) < 1e-4, cuts
+
+
 @pytest.mark.parametrize("tau", [1.0, 16.0, 0.25])
 def test_decays_from_nearly_none_to_nearly_all(tau):
     """tau stretches the decays towards one (a long memory) or squeezes them towards zero; 300 tokens whole
