@@ -14,6 +14,7 @@ from .parts import standard as _standard_parts  # noqa: F401  (registers the shi
 from .parts import gated as _gated_parts, latent as _latent_parts  # noqa: F401
 from .parts import biased as _biased_parts, recurrent as _recurrent_parts  # noqa: F401
 from .parts import postnorm as _postnorm_parts, windowed as _windowed_parts  # noqa: F401
+from .parts import stream as _stream_parts  # noqa: F401
 from . import models  # noqa: F401  (registers the shipped architectures)
 
 __version__ = "0.1.0"

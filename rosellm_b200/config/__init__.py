@@ -15,6 +15,7 @@ from .gpt2 import GPT2Config
 from .lebedra import LebedraConfig
 from .porovik import PorovikConfig
 from .fikevik import FikevikConfig
+from .soporax import SoporaxConfig
 
 __all__ = [
     "Architecture",
@@ -23,6 +24,8 @@ __all__ = [
     "GPT2Config",
     "LebedraConfig",
     "PorovikConfig",
+    "FikevikConfig",
+    "SoporaxConfig",
     "ModelConfig",
     "load_config",
     "parse_config",

@@ -8,7 +8,10 @@
 //   head_scale  : a further factor of the score per head, from a table            (absent: 1)
 //   window      : a query at i sees the keys j with 0 <= i - j < window            (0: all keys j <= i);
 //                 pages that lie wholly before a block's window are never looked up (the cache gives them back)
-//   out         = softmax(score) V * sigmoid(gate)                             (gate absent: no gate)
+//   sink        : one more term exp(sink_h) in the softmax's denominator, a table with one entry a head; it
+//                 has no key and no value and is not scaled                       (absent: a plain softmax)
+//   out         = softmax(score) V * sigmoid(gate)                             (gate absent: no gate); the gate's
+//                 logits are one a value column, or (gate_per_head) one a head
 //
 // Scores, softmax and the weighted sums are float32 whatever the cache holds.  Queries and gate logits are
 // float32 columns of the layer's packed projections.
@@ -53,7 +56,16 @@ struct BiasAttnParams {
   int n_splits;
   float* part_o;
   float* part_ml;
+  const float* sink;  // [n_heads] or null
+  int gate_per_head;  // the gate holds one logit a (token, head): [tokens, ldg], head h at column h
 };
+
+// The gate's logits of a (token, head): a pointer to the head's dv logits (stride 1), or to its one logit (stride 0).
+__device__ __forceinline__ const float* bias_gate_row(const BiasAttnParams& p, int tok, int head, int& stride) {
+  stride = p.gate_per_head ? 0 : 1;
+  if (p.gate == nullptr) return nullptr;
+  return p.gate + (size_t)tok * p.ldg + (p.gate_per_head ? (size_t)head : (size_t)head * p.dv);
+}
 
 }  // namespace rl
 
@@ -271,15 +283,16 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
   for (int a = 0; a < RPT; ++a) {
     if (!row_ok[a]) continue;
     const int tok = t_begin + first + (ty * RPT + a) / HB;
-    const float inv = 1.0f / l[a];
+    const float inv = 1.0f / (l[a] + (p.sink != nullptr ? expf(p.sink[row_head[a]] - m[a]) : 0.f));
     TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)row_head[a] * dv;
-    const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)row_head[a] * dv : nullptr;
+    int gs;
+    const float* gr = bias_gate_row(p, tok, row_head[a], gs);
 #pragma unroll
     for (int c = 0; c < DVC; ++c) {
       const int col = tx + LPR * c;
       if (col < dv) {
         float v = acc[a][c] * inv;
-        if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col]));
+        if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col * gs]));
         o[col] = from_f32<TOut>(v);
       }
     }
@@ -304,8 +317,10 @@ __global__ __launch_bounds__(128) void bias_attn_merge_kernel(const BiasAttnPara
   const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
   float L = 0.f;  // summed in the parts' order, by every lane alike
   for (int s = 0; s < p.n_splits; ++s) L = fmaf(__shfl_sync(0xffffffffu, ls, s), __shfl_sync(0xffffffffu, w, s), L);
+  if (p.sink != nullptr) L += expf(p.sink[head] - M);  // the sink counts once, after the parts
   TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)head * dv;
-  const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)head * dv : nullptr;
+  int gs;
+  const float* gr = bias_gate_row(p, tok, head, gs);
   for (int c0 = 0; c0 < dv; c0 += 32) {
     const int c = c0 + lane;
     float acc = 0.f;
@@ -315,7 +330,7 @@ __global__ __launch_bounds__(128) void bias_attn_merge_kernel(const BiasAttnPara
     }
     if (c < dv) {
       float v = acc / L;
-      if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[c]));
+      if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[c * gs]));
       o[c] = from_f32<TOut>(v);
     }
   }
@@ -419,6 +434,7 @@ RL_EXPORT int rl_bias_attention_shape(int heads_per_group, int rows, int* heads_
 // kernel; part_o float32 [n_decode * heads * n_splits, dv], part_ml float32 [n_decode * heads * n_splits, 2].
 // tensor_cores: prompt tiles go to `bias_attn_mma_kernel` where the types and sizes allow (64 rows a block: the
 // tiles must then be cut as rl_bias_attention_shape(.., 64, ..) says).
+// sink: float32 [heads] or null; gate_per_head: the gate's rows hold one logit a head, not one a value column.
 // tiles: (request, first new token) of portions cut every `tile_tokens` tokens (a multiple of the tokens a
 // block takes); decode_reqs: the requests that bring one token.  cache_dtype: the pool's element type;
 // out_dtype: that of out.
@@ -429,7 +445,7 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
                                 int dv, int v_at, int row, int page_size, int max_pages, float scale, float temp_coef,
                                 int temp_every, const float* slopes, int* status, int n_splits, float* part_o,
                                 float* part_ml, int tensor_cores, int window, const float* head_scale,
-                                cudaStream_t stream) {
+                                const float* sink, int gate_per_head, cudaStream_t stream) {
   if (n_tiles <= 0 && n_decode <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || v_at < dk ||
       v_at + dv > row || n_kv > 65535 || window < 0)
@@ -445,7 +461,8 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
   const int hg = n_heads / n_kv;
   rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
                        n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
-                       tt, hb, 0, scale, temp_coef, temp_every, slopes, status, window, head_scale, 1, part_o, part_ml};
+                       tt, hb, 0, scale, temp_coef, temp_every, slopes, status, window, head_scale, 1, part_o, part_ml,
+                       sink, gate_per_head != 0};
   if (p.n_tiles > 0) {  // the prompt portions: 32 or 64 rows a block, cut into tokens and heads as rl_bias_attention_shape says
     const dim3 grid(p.n_tiles * (tile_tokens / tt), n_kv, (hg + hb - 1) / hb);
     if (mma) rl::dispatch_bias_attn_mma(p, grid, stream);
@@ -498,7 +515,8 @@ namespace rl {
 // float32 columns of the packed projections, a warp a (token, head); a token's heads are spread over the blocks
 // of grid row y, so that a step of few tokens is as many short chains side by side, not one long one:
 //   queries and keys: each head's entries divided by their root mean square (eps inside the root) and
-//     multiplied by a weight the heads share (q_norm / k_norm; absent: left as they are), then the first
+//     multiplied by a weight the heads share (q_norm / k_norm; absent: left as they are, or with `unit_qk`
+//     divided by the root mean square and no weight), then the first
 //     `rot_dims` entries turned, entry 2i with entry 2i + 1, by the angle position * freq[i];
 //   values: each head's entries divided by their root mean square, no weight (unit_values; else untouched).
 // Angles are formed and evaluated in float32.
@@ -509,7 +527,7 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
                                                               const float* __restrict__ freq,
                                                               const int* __restrict__ positions, int n_tokens,
                                                               int n_heads, int n_kv, int dk, int dv, int rot_dims,
-                                                              int unit_values, float eps) {
+                                                              int unit_values, int unit_qk, float eps) {
   pdl_begin();
   const int tok = blockIdx.x;
   if (tok >= n_tokens) return;
@@ -526,7 +544,7 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
       float* e = is_q ? q + (size_t)tok * ldq + (size_t)u * dk : k + (size_t)tok * ldk + (size_t)(u - n_heads) * dk;
       const float* w = is_q ? q_norm : k_norm;
       float r = 1.0f;
-      if (w != nullptr) {
+      if (w != nullptr || unit_qk) {
         float ss = 0.f;
         for (int d = lane; d < dk; d += 32) ss = fmaf(e[d], e[d], ss);
         r = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
@@ -561,10 +579,12 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
 
 // Queries [tokens, heads * dk], keys [tokens, kv heads * dk] and values [tokens, kv heads * dv] (float32, row
 // strides given) normalised and rotated in place; see the kernel.  q_norm / k_norm: float32 [dk] or null (both
-// or neither); freq: float32 [rot_dims / 2] (rot_dims even, at most dk; 0: no rotation).
+// or neither; unit_qk: without weights, queries and keys are still divided by their root mean square);
+// freq: float32 [rot_dims / 2] (rot_dims even, at most dk; 0: no rotation).
 RL_EXPORT int rl_qkv_norm_rotate(float* q, long ldq, float* k, long ldk, float* v, long ldv, const float* q_norm,
                                  const float* k_norm, const float* freq, const int* positions, int n_tokens, int n_heads,
-                                 int n_kv, int dk, int dv, int rot_dims, int unit_values, float eps, cudaStream_t stream) {
+                                 int n_kv, int dk, int dv, int rot_dims, int unit_values, int unit_qk, float eps,
+                                 cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || dk <= 0 || dv <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > dk ||
       rot_dims > 256 || (rot_dims > 0 && freq == nullptr) || (q_norm == nullptr) != (k_norm == nullptr))
@@ -574,7 +594,7 @@ RL_EXPORT int rl_qkv_norm_rotate(float* q, long ldq, float* k, long ldk, float* 
   const int want = (148 * 40 + n_tokens - 1) / n_tokens, most = units < 4 * 1024 ? (units + 3) / 4 : 1024;
   const int rows = want < most ? want : most;
   rl::launch_pdl(rl::qkv_norm_rotate_kernel, dim3(n_tokens, rows), 128, 0, stream, q, ldq, k, ldk, v, ldv, q_norm, k_norm,
-                 freq, positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, eps);
+                 freq, positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, unit_qk, eps);
   RL_CHECK_LAUNCH();
   return 0;
 }

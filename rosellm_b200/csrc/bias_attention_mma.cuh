@@ -226,9 +226,10 @@ __global__ __launch_bounds__(BM_THREADS) void bias_attn_mma_kernel(const BiasAtt
     if (!row_ok[a]) continue;
     const int r = warp * 16 + quad + 8 * a;
     const int tok = t_begin + first + r / HB;
-    const float inv = 1.0f / l[a];
+    const float inv = 1.0f / (l[a] + (p.sink != nullptr ? expf(p.sink[row_head[a]] - m[a]) : 0.f));
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)tok * p.ldo + (size_t)row_head[a] * dv;
-    const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)row_head[a] * dv : nullptr;
+    int gs;
+    const float* gr = bias_gate_row(p, tok, row_head[a], gs);
 #pragma unroll
     for (int nt = 0; nt < DVT; ++nt) {
 #pragma unroll
@@ -236,7 +237,7 @@ __global__ __launch_bounds__(BM_THREADS) void bias_attn_mma_kernel(const BiasAtt
         const int col = nt * 8 + 2 * in_quad + e;
         if (col < dv) {
           float v = o[nt][2 * a + e] * inv;
-          if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col]));
+          if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col * gs]));
           out[col] = __float2bfloat16_rn(v);
         }
       }

@@ -45,7 +45,7 @@ __global__ __launch_bounds__(128) void latent_kv_write_kernel(
     const float* __restrict__ inv_freq, int rot_dims, T* __restrict__ pool, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ positions, const int* __restrict__ req_of_token,
     const int* __restrict__ slots, int n_tokens, int rank, int rot_dim, int row_width, int page_size, int max_pos,
-    int* __restrict__ status) {
+    float rot_mult, int* __restrict__ status) {
   __shared__ float scratch[33];
   pdl_begin();
   const int n = blockIdx.x;
@@ -73,7 +73,7 @@ __global__ __launch_bounds__(128) void latent_kv_write_kernel(
     float v = 0.f;
     if (j < rot_dims) {
       const int i = j >> 1;
-      v = rotate_element(kr[2 * i], kr[2 * i + 1], (float)pos * inv_freq[i], j & 1);
+      v = rotate_element(kr[2 * i], kr[2 * i + 1], (float)pos * inv_freq[i], j & 1) * rot_mult;
     } else if (j < rot_dim) {
       v = kr[j];
     }
@@ -87,7 +87,7 @@ template <typename T>
 __global__ __launch_bounds__(128) void latent_q_rope_kernel(
     const T* __restrict__ q, long q_stride, int head_in, int plain, T* __restrict__ rows, long rows_stride,
     int row_width, int rank, int rot_dim, int rot_dims, const float* __restrict__ inv_freq,
-    const int* __restrict__ positions, int n_tokens, int n_heads) {
+    const int* __restrict__ positions, int n_tokens, int n_heads, float rot_mult) {
   pdl_begin();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
@@ -99,7 +99,7 @@ __global__ __launch_bounds__(128) void latent_q_rope_kernel(
     float v = 0.f;
     if (j < rot_dims) {
       const int pair = j >> 1;
-      v = rotate_element(to_f32(qr[2 * pair]), to_f32(qr[2 * pair + 1]), pos * inv_freq[pair], j & 1);
+      v = rotate_element(to_f32(qr[2 * pair]), to_f32(qr[2 * pair + 1]), pos * inv_freq[pair], j & 1) * rot_mult;
     } else if (j < rot_dim) {
       v = to_f32(qr[j]);
     }
@@ -824,12 +824,13 @@ RL_EXPORT int rl_latent_decode_fits(int n_heads, int rank, int row_width) {
 }
 
 // dkv: float32 [tokens, >= rank + rot_dim] with row stride ld: the first `rank` entries are
-// normalised (gamma, eps), the next `rot_dim` rotated in their first `rot_dims` entries.
+// normalised (gamma, eps), the next `rot_dim` rotated in their first `rot_dims` entries; rot_mult: a factor
+// of the cosines and sines (of the turned entries), 1 for a plain rotation.
 RL_EXPORT int rl_latent_kv_write(int dtype, const float* dkv, long ld, const float* gamma, float eps,
                                  const float* inv_freq, int rot_dims, void* pool, const int* block_table,
                                  int bt_stride, const int* positions, const int* req_of_token, const int* slots,
                                  int n_tokens, int rank, int rot_dim, int row_width, int page_size, int max_pos,
-                                 int* status, cudaStream_t stream) {
+                                 float rot_mult, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || row_width < rank + rot_dim ||
       status == nullptr)
@@ -837,11 +838,11 @@ RL_EXPORT int rl_latent_kv_write(int dtype, const float* dkv, long ld, const flo
   if (dtype == RL_F32)
     rl::launch_pdl(rl::latent_kv_write_kernel<float>, n_tokens, 128, 0, stream, dkv, ld, gamma, eps, inv_freq, rot_dims,
                    (float*)pool, block_table, bt_stride, positions, req_of_token, slots, n_tokens, rank, rot_dim,
-                   row_width, page_size, max_pos, status);
+                   row_width, page_size, max_pos, rot_mult, status);
   else
     rl::launch_pdl(rl::latent_kv_write_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, dkv, ld, gamma, eps, inv_freq,
                    rot_dims, (__nv_bfloat16*)pool, block_table, bt_stride, positions, req_of_token, slots, n_tokens,
-                   rank, rot_dim, row_width, page_size, max_pos, status);
+                   rank, rot_dim, row_width, page_size, max_pos, rot_mult, status);
   RL_CHECK_LAUNCH();
   return 0;
 }
@@ -851,16 +852,17 @@ RL_EXPORT int rl_latent_kv_write(int dtype, const float* dkv, long ld, const flo
 RL_EXPORT int rl_latent_q_rope(int dtype, const void* q, long q_stride, int head_in, int plain, void* rows,
                                long rows_stride, int row_width, int rank, int rot_dim, int rot_dims,
                                const float* inv_freq, const int* positions, int n_tokens, int n_heads,
-                               cudaStream_t stream) {
+                               float rot_mult, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (rot_dims > rot_dim || (rot_dims & 1) || row_width < rank + rot_dim || plain + rot_dim > head_in) return -2;
   if (dtype == RL_F32)
     rl::launch_pdl(rl::latent_q_rope_kernel<float>, n_tokens, 128, 0, stream, (const float*)q, q_stride, head_in, plain,
-                   (float*)rows, rows_stride, row_width, rank, rot_dim, rot_dims, inv_freq, positions, n_tokens, n_heads);
+                   (float*)rows, rows_stride, row_width, rank, rot_dim, rot_dims, inv_freq, positions, n_tokens, n_heads,
+                   rot_mult);
   else
     rl::launch_pdl(rl::latent_q_rope_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, (const __nv_bfloat16*)q, q_stride,
                    head_in, plain, (__nv_bfloat16*)rows, rows_stride, row_width, rank, rot_dim, rot_dims, inv_freq,
-                   positions, n_tokens, n_heads);
+                   positions, n_tokens, n_heads, rot_mult);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -130,6 +130,36 @@ __global__ __launch_bounds__(128) void moe_select_kernel(const float* __restrict
   }
 }
 
+// Routing without a router: row `token id` of an integer table [vocab, top] names the token's experts (the entries
+// of a row differ), each with the same weight.  A thread a (token, choice); ids, weights and counts as
+// `moe_select_kernel` leaves them.  An id below zero is row -id - 1 of the engine's token feedback.
+__global__ __launch_bounds__(256) void moe_table_select_kernel(const int* __restrict__ token_ids,
+                                                               const int* __restrict__ table, int vocab, int n_tokens,
+                                                               int n_experts, int top, float weight, int* __restrict__ ids,
+                                                               float* __restrict__ weights, int* __restrict__ counts,
+                                                               const int* __restrict__ feedback, int n_feedback,
+                                                               int* __restrict__ status) {
+  pdl_begin();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * top) return;
+  const int t = i / top, j = i - t * top;
+  int id = token_ids[t];
+  if (id < 0 && feedback != nullptr && -id - 1 < n_feedback) id = feedback[-id - 1];
+  int e = 0;
+  if (id < 0 || id >= vocab) {
+    atomicOr(status, RL_STATUS_BAD_TOKEN);
+  } else {
+    e = table[(size_t)id * top + j];
+    if (e < 0 || e >= n_experts) {
+      atomicOr(status, RL_STATUS_BAD_TOKEN);
+      e = 0;
+    }
+  }
+  ids[i] = e;
+  weights[i] = weight;
+  atomicAdd(&counts[e], 1);
+}
+
 // One block.  offsets[e]: first place of expert e; tiles[k] = (expert, first place, rows);
 // meta[0]: number of tiles.  Leaves counts and fill zero (the scatter that follows counts the
 // places it hands out in fill).
@@ -414,6 +444,18 @@ RL_EXPORT int rl_moe_select(const float* z, long ldz, const float* correction, i
     cudaFuncSetAttribute(rl::moe_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   rl::launch_pdl(rl::moe_select_kernel, (n_tokens + 3) / 4, 128, smem, stream, z, ldz, correction, n_tokens, n_experts,
                  top, group_count, group_keep, score_kind, ids, weights, counts);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// table: int32 [vocab, top]; every chosen expert gets `weight`.  ids, weights, counts as rl_moe_select leaves them.
+RL_EXPORT int rl_moe_table_select(const int* token_ids, const int* table, int vocab, int n_tokens, int n_experts, int top,
+                                  float weight, int* ids, float* weights, int* counts, const int* feedback, int n_feedback,
+                                  int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (n_experts <= 0 || n_experts > 2048 || top <= 0 || top > n_experts || vocab <= 0 || status == nullptr) return -2;
+  rl::launch_pdl(rl::moe_table_select_kernel, (n_tokens * top + 255) / 256, 256, 0, stream, token_ids, table, vocab,
+                 n_tokens, n_experts, top, weight, ids, weights, counts, feedback, n_feedback, status);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -85,6 +85,8 @@ def _parts_with_specs(spec: ModelSpec, model: "Model | None" = None):
             one(cat, ps, layer.parts[name] if layer else None)
     one("norm", spec.final_norm, model.final_norm if model else None)
     one("head", spec.head, model.head if model else None)
+    for i, ps in enumerate(spec.stream_parts):
+        one("stream_input", ps, model.stream_parts[i] if model else None)
     return pairs
 
 
@@ -106,6 +108,14 @@ class Model:
         self.layers = [_build_layer(ls) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
+        # what is added to the stream between runs of layers: the parts, and per position of the run order the
+        # (part, arguments) that come right before it
+        self.stream_parts = [build_part("stream_input", ps) for ps in spec.stream_parts]
+        self._stream_before: dict[int, list] = {}
+        for si in spec.stream_inputs:
+            self._stream_before.setdefault(si.before, []).append((self.stream_parts[si.part], dict(si.args)))
+        first = {id(p) for p, _ in self._stream_before.get(0, [])[:1]}  # it sees the embedding's output itself
+        self._stream_keepers = [p for p in self.stream_parts if id(p) not in first and hasattr(p, "keep_embedding")]
         self.loaded = False
         self._keyed_parts: list | None = None
 
@@ -225,8 +235,12 @@ class Model:
         logits are made: ``None`` then too."""
         ctx.position = self.position
         x = self.embedding.forward(ctx, self.position)
+        for part in self._stream_keepers:
+            part.keep_embedding(ctx, x)
         order = self.spec.run_order
         for i, run in enumerate(order):
+            for k, (part, args) in enumerate(self._stream_before.get(i, ())):
+                part.forward(ctx, x, first=(i == 0 and k == 0), **args)
             layer = self.layers[run.layer]
             # a block may finish with work of the layer that runs next (its first norm, say): it finds that layer here
             ctx.extras["next_layer"] = self.layers[order[i + 1].layer] if i + 1 < len(order) else None

@@ -157,8 +157,8 @@ def _lib() -> ctypes.CDLL:
         lib.rl_cast_rows.argtypes = [P, P, L, P]
         lib.rl_latent_attention_fits.argtypes = [I, I, I]
         lib.rl_latent_decode_fits.argtypes = [I, I, I]
-        lib.rl_latent_kv_write.argtypes = [I, P, L, P, F, P, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
-        lib.rl_latent_q_rope.argtypes = [I, P, L, I, I, P, L, I, I, I, I, P, P, I, I, P]
+        lib.rl_latent_kv_write.argtypes = [I, P, L, P, F, P, I, P, P, I, P, P, P, I, I, I, I, I, I, F, P, P]
+        lib.rl_latent_q_rope.argtypes = [I, P, L, I, I, P, L, I, I, I, I, P, P, I, I, F, P]
         lib.rl_latent_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, P, I, I, I, I, F, P, I, P, I, I, I, P, P, I, P, P]
         lib.rl_head_linear.argtypes = [I, P, L, L, P, L, L, L, P, L, L, I, I, I, I, P]
         lib.rl_gated_act.argtypes = [I, P, L, I, P, L, I, I, I, F, F, P]
@@ -174,15 +174,19 @@ def _lib() -> ctypes.CDLL:
         lib.rl_recurrence_record.argtypes = [I, I, I, P, P, P]
         lib.rl_bias_attention_shape.argtypes = [I, I, P, P]
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
-                                          F, F, I, P, P, I, P, P, I, I, P, P]
-        lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, F, P]
+                                          F, F, I, P, P, I, P, P, I, I, P, P, I, P]
+        lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
+        lib.rl_stream_inject.argtypes = [P, L, P, P, L, P, L, I, I, P]
+        lib.rl_gate_mul.argtypes = [I, P, L, P, L, I, I, P]
+        lib.rl_moe_table_select.argtypes = [P, P, I, I, I, I, F, P, P, P, P, I, P, P]
         lib.rl_gated_join_norm.argtypes = [P, L, F, P, L, F, P, L, P, P, P, L, P, L, I, I, F, F, P]
         lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
                      "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts", "rl_embed_pair",
                      "rl_rmsnorm_add_norm", "rl_recurrence", "rl_recurrence_record", "rl_bias_attention_shape", "rl_bias_attention",
-                     "rl_bias_kv_store", "rl_qkv_norm_rotate", "rl_gated_join_norm"):
+                     "rl_bias_kv_store", "rl_qkv_norm_rotate", "rl_gated_join_norm", "rl_stream_inject", "rl_gate_mul",
+                     "rl_moe_table_select"):
             getattr(lib, name).restype = I
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
@@ -998,11 +1002,12 @@ def latent_decode_fits(n_heads: int, rank: int, row_width: int) -> bool:
 
 
 def latent_kv_write(dkv, gamma, eps: float, inv_freq, rot_dims: int, pool, block_table, positions, req_of_token, slots,
-                    *, rank: int, rot_dim: int, max_pos: int) -> None:
+                    *, rank: int, rot_dim: int, max_pos: int, rot_mult: float = 1.0) -> None:
     """The step's cache rows: ``dkv`` float32 [tokens, rank + rot_dim]; the first ``rank`` entries
     RMS-normalised (``gamma``, ``eps``), the next ``rot_dim`` rotated by the token's position in
     their first ``rot_dims`` entries (pairs (2i, 2i+1), angle position * inv_freq[i]); written to
-    ``pool`` [pages, 1, 1, page size, row width] in the pool's dtype, zeros beyond."""
+    ``pool`` [pages, 1, 1, page size, row width] in the pool's dtype, zeros beyond.  ``rot_mult``: a factor of the
+    cosines and sines."""
     _need(dkv, "dkv", torch.float32, contiguous=False)
     _need(gamma, "gamma", torch.float32)
     _need(pool, "pool")
@@ -1017,12 +1022,12 @@ def latent_kv_write(dkv, gamma, eps: float, inv_freq, rot_dims: int, pool, block
     rc = _lib().rl_latent_kv_write(_code(pool), _ptr(dkv), dkv.stride(0), _ptr(gamma), float(eps), _ptr(inv_freq),
                                    rot_dims, _ptr(pool), _ptr(block_table), block_table.stride(0), _ptr(positions),
                                    _ptr(req_of_token), _ptr(slots), dkv.shape[0], rank, rot_dim, row_width, page_size,
-                                   max_pos, _ptr(status_word(pool.device)), _stream())
+                                   max_pos, float(rot_mult), _ptr(status_word(pool.device)), _stream())
     _ok(rc, "latent_kv_write")
 
 
 def latent_q_rope(q, rows, inv_freq, positions, *, n_heads: int, head_in: int, plain: int, rank: int, rot_dim: int,
-                  rot_dims: int, row_width: int) -> None:
+                  rot_dims: int, row_width: int, rot_mult: float = 1.0) -> None:
     """rows[t, h, rank:row_width] = the rotated part of head h's query (q[t, h*head_in + plain:
     ... + rot_dim]) turned by positions[t], then zeros."""
     _need(q, "q", contiguous=False)
@@ -1031,7 +1036,8 @@ def latent_q_rope(q, rows, inv_freq, positions, *, n_heads: int, head_in: int, p
     if q.shape[1] != n_heads * head_in or rows.shape[1] != n_heads * row_width or q.stride(1) != 1 or rows.stride(1) != 1:
         raise KernelError("latent_q_rope: widths do not fit the heads")
     rc = _lib().rl_latent_q_rope(_code(q), _ptr(q), q.stride(0), head_in, plain, _ptr(rows), rows.stride(0), row_width,
-                                 rank, rot_dim, rot_dims, _ptr(inv_freq), _ptr(positions), n, n_heads, _stream())
+                                 rank, rot_dim, rot_dims, _ptr(inv_freq), _ptr(positions), n, n_heads, float(rot_mult),
+                                 _stream())
     _ok(rc, "latent_q_rope")
 
 
@@ -1101,6 +1107,36 @@ def gated_act(gu, out, *, width: int, up_at: int, gate: int, alpha: float = 1.0,
                             gate, float(alpha), float(limit), _stream()), "gated_act")
 
 
+def gate_mul(o, g) -> None:
+    """o <- o * sigmoid(g) in place: ``o`` [rows, width] float32 or bfloat16, ``g`` float32 logits of the same shape;
+    both may be views with a row stride."""
+    _need(o, "o", contiguous=False)
+    _need(g, "g", torch.float32, contiguous=False)
+    if tuple(o.shape) != tuple(g.shape) or o.stride(1) != 1 or g.stride(1) != 1:
+        raise KernelError("gate_mul: shapes differ, or rows are not contiguous")
+    _ok(_lib().rl_gate_mul(_code(o), _ptr(o), o.stride(0), _ptr(g), g.stride(0), o.shape[0], o.shape[1], _stream()), "gate_mul")
+
+
+def stream_inject(x, vec=None, again=None, keep=None) -> None:
+    """``keep <- x`` (where given), then ``x <- x + vec + again``: ``x``, ``again``, ``keep`` float32 [rows, width],
+    ``vec`` float32 [width] added to every row; any of the three may be ``None``."""
+    _need(x, "x", torch.float32, contiguous=False)
+    n, width = x.shape
+    if vec is not None:
+        _need(vec, "vec", torch.float32)
+        if vec.numel() != width:
+            raise KernelError("stream_inject: the row to add has another width")
+    for t, name in ((again, "again"), (keep, "keep")):
+        if t is not None:
+            _need(t, name, torch.float32, contiguous=False)
+            if tuple(t.shape) != (n, width) or t.stride(1) != 1:
+                raise KernelError(f"stream_inject: {name} has another shape")
+    if x.stride(1) != 1 or (again is not None and keep is not None and again.data_ptr() == keep.data_ptr()):
+        raise KernelError("stream_inject: rows must be contiguous, and the rows kept are not the rows added")
+    _ok(_lib().rl_stream_inject(_ptr(x), x.stride(0), _ptr(vec), _ptr(again), 0 if again is None else again.stride(0),
+                                _ptr(keep), 0 if keep is None else keep.stride(0), n, width, _stream()), "stream_inject")
+
+
 def token_gate(s, token_ids, table, col0: int, dim: int, out, feedback=None) -> None:
     """out[n, j] = gelu_tanh(s[n, j]) * table[token_ids[n], col0 + j] for j < dim, zero beyond."""
     _need(s, "s", contiguous=False)
@@ -1138,6 +1174,25 @@ def moe_select(z, correction, *, top: int, group_count: int, group_keep: int, id
     if rc in (-2, -3):
         raise KernelError(f"moe_select: {n_experts} experts, top {top}, {group_keep} of {group_count} groups not taken")
     _ok(rc, "moe_select")
+
+
+def moe_table_select(token_ids, table, *, n_experts: int, weight: float, ids, weights, counts, feedback=None) -> None:
+    """Routing by a table: row ``token_ids[t]`` of ``table`` (int32 [vocab, top]) names token t's experts, each with
+    ``weight``.  ``ids``, ``weights``, ``counts`` as ``moe_select`` leaves them (``counts`` zero on entry)."""
+    _need(token_ids, "token_ids", torch.int32)
+    _need(table, "table", torch.int32)
+    for t, name, dt in ((ids, "ids", torch.int32), (weights, "weights", torch.float32), (counts, "counts", torch.int32)):
+        _need(t, name, dt)
+    vocab, top = table.shape
+    n = token_ids.numel()
+    if ids.numel() < n * top or weights.numel() < n * top or counts.numel() < n_experts:
+        raise KernelError("moe_table_select: the outputs are too small")
+    rc = _lib().rl_moe_table_select(_ptr(token_ids), _ptr(table), vocab, n, n_experts, top, float(weight), _ptr(ids),
+                                    _ptr(weights), _ptr(counts), _ptr(feedback), 0 if feedback is None else feedback.numel(),
+                                    _ptr(status_word(table.device)), _stream())
+    if rc == -2:
+        raise KernelError(f"moe_table_select: {n_experts} experts, {top} a token not taken")
+    _ok(rc, "moe_table_select")
 
 
 def moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, *, n_tokens: int, n_experts: int, top: int,
@@ -1349,7 +1404,8 @@ def bias_kv_store(k, v, pool, block_table, positions, req_of_token, slots, *, v_
 def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, dk: int, dv: int, v_at: int,
                    scale: float, slopes=None, temp_coef: float = 0.0, temp_every: int = 0, tiles=None, n_tiles: int = 0,
                    tile_tokens: int = 16, decode_reqs=None, n_decode: int = 0, max_pos: int, n_splits: int = 1, part_o=None,
-                   part_ml=None, tensor_cores: bool = False, window: int = 0, head_scale=None) -> None:
+                   part_ml=None, tensor_cores: bool = False, window: int = 0, head_scale=None, sink=None,
+                   gate_per_head: bool = False) -> None:
     """Causal attention of the step's queries over the cached rows (csrc/bias_attention.cu).
     ``tensor_cores``: prompt portions on mma.sync (bfloat16 pool and output, sizes up to 128; the tiles cut as
     ``bias_attention_shape(.., True)`` says).
@@ -1358,7 +1414,8 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
     ``q`` float32 [tokens, heads * dk] and ``gate`` float32 [tokens, heads * dv] (or ``None``) may be views
     with a row stride; ``out`` [tokens, heads * dv] float32 or bfloat16; ``slopes`` float32 [heads] or ``None``.
     ``window`` > 0: a query sees itself and the ``window - 1`` keys before it; ``head_scale`` float32 [heads]: a
-    further factor of every score of a head."""
+    further factor of every score of a head; ``sink`` float32 [heads]: one more term exp(sink[h]) in the softmax's
+    denominator (no key, no value, not scaled); ``gate_per_head``: ``gate`` is [tokens, heads], one logit a head."""
     _need(q, "q", torch.float32, contiguous=False)
     _need(out, "out", contiguous=False)
     _need(pool, "pool")
@@ -1367,9 +1424,9 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
         raise KernelError("bias_attention: shapes do not fit")
     if gate is not None:
         _need(gate, "gate", torch.float32, contiguous=False)
-        if gate.shape[1] != n_heads * dv or gate.stride(1) != 1:
+        if gate.shape[1] != (n_heads if gate_per_head else n_heads * dv) or gate.stride(1) != 1:
             raise KernelError("bias_attention: the gate has another shape")
-    for t, name in ((slopes, "slopes"), (head_scale, "head_scale")):
+    for t, name in ((slopes, "slopes"), (head_scale, "head_scale"), (sink, "sink")):
         if t is not None:
             _need(t, name, torch.float32)
             if t.numel() != n_heads:
@@ -1390,7 +1447,7 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
                                   int(temp_every), _ptr(slopes), _ptr(status_word(out.device)), int(n_splits), _ptr(part_o),
                                   _ptr(part_ml), int(bool(tensor_cores) and bias_attention_tensor_cores(pool.dtype, dk, dv)
                                                      and out.dtype == torch.bfloat16), int(window), _ptr(head_scale),
-                                  _stream())
+                                  _ptr(sink), int(bool(gate_per_head)), _stream())
     if rc in (-2, -3, -4):
         raise KernelError(f"bias_attention: sizes not taken (code {rc}: key and value sizes up to 256; tiles a multiple "
                           "of the tokens a block takes)")
@@ -1398,11 +1455,12 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
 
 
 def qkv_norm_rotate(q, k, v, positions, *, n_heads: int, n_kv: int, dk: int, dv: int, eps: float, q_norm=None, k_norm=None,
-                    freq=None, rot_dims: int = 0, unit_values: bool = False) -> None:
+                    freq=None, rot_dims: int = 0, unit_values: bool = False, unit_qk: bool = False) -> None:
     """In place on float32 views (row strides allowed): every head of ``q`` [tokens, heads * dk] and ``k``
     [tokens, kv heads * dk] divided by its root mean square and multiplied by ``q_norm`` / ``k_norm`` (float32
     [dk], both or neither), then its first ``rot_dims`` entries turned in neighbouring pairs by position *
-    ``freq[i]``; with ``unit_values`` every head of ``v`` [tokens, kv heads * dv] divided by its root mean square."""
+    ``freq[i]``; with ``unit_values`` every head of ``v`` [tokens, kv heads * dv] divided by its root mean square;
+    with ``unit_qk`` (and no weights) every head of q and k divided by its root mean square and left so."""
     for t, name, width in ((q, "q", n_heads * dk), (k, "k", n_kv * dk), (v, "v", n_kv * dv)):
         _need(t, name, torch.float32, contiguous=False)
         if t.shape[1] != width or t.stride(1) != 1 or t.shape[0] != q.shape[0]:
@@ -1418,7 +1476,7 @@ def qkv_norm_rotate(q, k, v, positions, *, n_heads: int, n_kv: int, dk: int, dv:
             raise KernelError("qkv_norm_rotate: one frequency a turned pair")
     rc = _lib().rl_qkv_norm_rotate(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(q_norm), _ptr(k_norm),
                                    _ptr(freq) if rot_dims else None, _ptr(positions), q.shape[0], n_heads, n_kv, dk, dv,
-                                   int(rot_dims), int(bool(unit_values)), float(eps), _stream())
+                                   int(rot_dims), int(bool(unit_values)), int(bool(unit_qk)), float(eps), _stream())
     if rc == -2:
         raise KernelError("qkv_norm_rotate: sizes not taken (an even number of turned entries, at most the key size; "
                           "both norms or neither)")

@@ -8,7 +8,7 @@ from .base import (
     register_part,
     unregister_part,
 )
-from .spec import Concat, LayerSpec, ModelSpec, PartSpec, RunEntry
+from .spec import Concat, LayerSpec, ModelSpec, PartSpec, RunEntry, StreamInput
 
 __all__ = [
     "Concat",
@@ -20,6 +20,7 @@ __all__ = [
     "PartSpec",
     "RunEntry",
     "StateSpec",
+    "StreamInput",
     "build_part",
     "part_class",
     "register_part",

@@ -24,6 +24,10 @@ Categories and the signature of ``forward``:
 ``block``          ``forward(ctx, run, layer, x)``: arranges norms, mixer and
                    feed-forward of one layer around the residual stream.
 ``head``           ``forward(ctx, h) -> logits`` ``[rows, vocab]`` float32.
+``stream_input``   ``forward(ctx, x, first=False, **args)``: adds something to the stream between two runs of
+                   layers (``ModelSpec.stream_inputs`` says where and with which ``args``; ``first``: the
+                   stream is the embedding's output as it stands); ``keep_embedding(ctx, x)`` is called
+                   right after the embedding for a part none of whose inputs comes first.
 """
 from __future__ import annotations
 
@@ -32,7 +36,7 @@ from typing import Any, Callable
 
 import torch
 
-CATEGORIES = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head")
+CATEGORIES = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head", "stream_input")
 
 _PARTS: dict[tuple[str, str], type] = {}
 
@@ -84,6 +88,8 @@ class ParamSpec:
     transpose: bool = False
     # how the random-weights mode fills it: "normal" or "ones" (a norm's scale)
     init: str = "normal"
+    # an integer table's entries lie in [0, below); the random-weights mode draws every row's entries distinct
+    below: int = 0
 
 
 @dataclass(frozen=True)

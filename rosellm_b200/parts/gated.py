@@ -71,6 +71,8 @@ class MixtureOfExperts(Part):
     ``group_count`` equal groups of neighbours) whose best choice score is largest; the chosen
     experts' outputs are summed with their scores ``s`` as weights (not renormalised); with
     ``weight_input`` the weight multiplies the expert's input instead: the sum of ``expert(s * h)``.
+    ``routing="table"``: no router; row ``token id`` of an integer table ``[vocab_size, top]`` (tensor ``table``; the
+    entries of a row differ) names the token's experts, each with weight ``1 / top``.
     Routing, the experts' layout and their products all run on the device
     (csrc/moe.cu): a step's launches follow from its token count alone.
     Experts' tensors: ``gate_up_weight`` [experts * 2 * inner, hidden] (per expert the gate rows,
@@ -82,7 +84,14 @@ class MixtureOfExperts(Part):
 
     def __init__(self, hidden_size: int, inner_size: int, num_experts: int, top: int, group_count: int = 1,
                  group_keep: int = 1, gate: str = "silu", alpha: float = 1.0, limit: float = 0.0,
-                 correction: bool = False, score: str = "softmax", weight_input: bool = False) -> None:
+                 correction: bool = False, score: str = "softmax", weight_input: bool = False,
+                 routing: str = "router", vocab_size: int = 0) -> None:
+        if routing not in ("router", "table"):
+            raise ValueError(f"mixture of experts: routing {routing!r}; 'router' or 'table'")
+        if routing == "table" and (vocab_size <= 0 or correction or group_count != 1):
+            raise ValueError("mixture of experts: a routing table needs the vocabulary's size and takes no "
+                             "correction and no groups")
+        self.routing, self.vocab_size = routing, int(vocab_size)
         if score not in K.MOE_SCORES:
             raise ValueError(f"mixture of experts: score {score!r}; one of {sorted(K.MOE_SCORES)}")
         self.score, self.weight_input = K.MOE_SCORES[score], bool(weight_input)
@@ -100,13 +109,16 @@ class MixtureOfExperts(Part):
         self.group_count, self.group_keep = group_count, group_keep
         self.gate, self.alpha, self.limit = _gate(gate), float(alpha), float(limit)
         self.has_correction = bool(correction)
-        self.router_weight = self.correction = self.gate_up_weight = self.down_weight = None
+        self.router_weight = self.correction = self.gate_up_weight = self.down_weight = self.table = None
 
     def param_specs(self):
         E, f, hid = self.num_experts, self.inner_size, self.hidden_size
-        specs = [ParamSpec("router_weight", (E, hid)),
-                 ParamSpec("gate_up_weight", (E * 2 * f, hid)),
+        specs = [ParamSpec("gate_up_weight", (E * 2 * f, hid)),
                  ParamSpec("down_weight", (E * hid, f))]
+        if self.routing == "table":
+            specs.append(ParamSpec("table", (self.vocab_size, self.top), kind="int_table", below=E))
+        else:
+            specs.insert(0, ParamSpec("router_weight", (E, hid)))
         if self.has_correction:
             specs.append(ParamSpec("correction", (E,), kind="vector"))
         return specs
@@ -114,14 +126,18 @@ class MixtureOfExperts(Part):
     def forward(self, ctx, h, x, add: bool = True) -> None:
         n, E, top, f, hid = ctx.n_tokens, self.num_experts, self.top, self.inner_size, self.hidden_size
         ws, i32 = ctx.workspace, torch.int32
-        z = ws.get("moe_logits", (n, E), torch.float32)
-        K.linear(h, self.router_weight, None, z)
         ids = ws.get("moe_ids", (n * top,), i32)
         weights = ws.get("moe_weights", (n * top,), torch.float32)
         counts = ws.get_zeroed("moe_counts", (E,), i32)
         fill = ws.get_zeroed("moe_fill", (E,), i32)
-        K.moe_select(z, self.correction, top=top, group_count=self.group_count, group_keep=self.group_keep, ids=ids,
-                     weights=weights, counts=counts, score=self.score)
+        if self.routing == "table":
+            K.moe_table_select(ctx.token_ids, self.table, n_experts=E, weight=1.0 / top, ids=ids, weights=weights,
+                               counts=counts, feedback=ctx.extras.get("token_feedback"))
+        else:
+            z = ws.get("moe_logits", (n, E), torch.float32)
+            K.linear(h, self.router_weight, None, z)
+            K.moe_select(z, self.correction, top=top, group_count=self.group_count, group_keep=self.group_keep, ids=ids,
+                         weights=weights, counts=counts, score=self.score)
         offsets = ws.get("moe_offsets", (E + 1,), i32)
         tiles = ws.get("moe_tiles", (K.moe_max_tiles(n * top, E) * 3,), i32)
         meta = ws.get("moe_meta", (4,), i32)

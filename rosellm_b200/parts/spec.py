@@ -148,6 +148,17 @@ class RunEntry:
 
 
 @dataclass(frozen=True)
+class StreamInput:
+    """Something added to the stream right before position ``before`` of the run order (0: between the
+    embedding and the first run): part ``part`` of ``ModelSpec.stream_parts`` (category ``stream_input``),
+    whose ``forward`` is handed ``args`` (which row of its table, say).  Several may name the same part."""
+
+    before: int
+    part: int = 0
+    args: tuple[tuple[str, Any], ...] = ()
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     hidden_size: int
     vocab_size: int
@@ -163,9 +174,15 @@ class ModelSpec:
     optional_prefixes: tuple[str, ...] = ()
     # glob patterns of tensors a file may hold that no part reads
     ignored_tensors: tuple[str, ...] = ()
+    # parts that add to the stream between runs of layers, and where each does
+    stream_parts: tuple[PartSpec, ...] = ()
+    stream_inputs: tuple[StreamInput, ...] = ()
 
     def __post_init__(self) -> None:
         n = len(self.layers)
+        for si in self.stream_inputs:
+            if not 0 <= si.before < len(self.run_order) or not 0 <= si.part < len(self.stream_parts):
+                raise ValueError(f"stream input {si}: before names a position of the run order, part one of stream_parts")
         seen_writer: set[int] = set()
         for pos, entry in enumerate(self.run_order):
             if not 0 <= entry.layer < n:

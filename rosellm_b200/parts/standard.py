@@ -59,11 +59,71 @@ def rotary_frequencies(dims: int, base: float) -> torch.Tensor:
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).to(torch.float32)
 
 
+ROTARY_SCALINGS = ("wavelength", "ramp")
+
+
+def scaled_rotary_frequencies(dims: int, base: float, scaling: dict | None) -> tuple[torch.Tensor, float]:
+    """(frequencies, factor of the cosines and sines) of a rotation whose frequencies are stretched for
+    sequences longer than ``scaling["original"]`` positions; float64 arithmetic, float32 result.
+
+    ``kind`` ``"wavelength"`` (``factor``, ``low``, ``high``, ``original``): a pair whose wavelength l = 2 pi / f
+    is below original / high keeps f; above original / low it turns ``factor`` times slower; between, with
+    s = (original / l - low) / (high - low), it gets (1 - s) f / factor + s f.
+
+    ``kind`` ``"ramp"`` (``factor``, ``original``, ``fast``, ``slow``): with index(t) = dims ln(original / (2 pi t)) /
+    (2 ln base), lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)), dims - 1) and r_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1), pair i gets r_i f_i / factor + (1 - r_i) f_i; cosines and sines are multiplied by
+    0.1 ln(factor) + 1."""
+    import math
+
+    f = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return torch.tensor(f, dtype=torch.float64).to(torch.float32), 1.0
+    kind = scaling.get("kind")
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    if factor <= 0 or original <= 0:
+        raise ValueError("rotary scaling: factor and original must be positive")
+    mult = 1.0
+    if kind == "wavelength":
+        low, high = float(scaling["low"]), float(scaling["high"])
+        if high == low:
+            raise ValueError("rotary scaling: low and high must differ")
+        out = []
+        for fi in f:
+            wave = 2.0 * math.pi / fi
+            if wave < original / high:
+                out.append(fi)
+            elif wave > original / low:
+                out.append(fi / factor)
+            else:
+                s = (original / wave - low) / (high - low)
+                out.append((1.0 - s) * fi / factor + s * fi)
+        f = out
+    elif kind == "ramp":
+        fast, slow = float(scaling["fast"]), float(scaling["slow"])
+        if fast <= 0 or slow <= 0 or base == 1.0:
+            raise ValueError("rotary scaling: fast and slow must be positive and the base not 1")
+
+        def index_of(turns: float) -> float:
+            return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+        lo = max(math.floor(index_of(fast)), 0)
+        hi = min(math.ceil(index_of(slow)), dims - 1)
+        ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(len(f))]
+        f = [fi / factor * r + fi * (1.0 - r) for fi, r in zip(f, ramp)]
+        mult = 0.1 * math.log(factor) + 1.0
+    else:
+        raise ValueError(f"rotary scaling kind {kind!r}; one of {ROTARY_SCALINGS}")
+    return torch.tensor(f, dtype=torch.float64).to(torch.float32), mult
+
+
 @register_part("position", "rotary")
 class RotaryPositions(Part):
     """Rotation of queries and keys by their positions: of every head's ``head_dim`` entries the
     first ``dims`` are turned, entry 2i with entry 2i+1 (the interleaved layout) by the angle
     position * base^(-2i/dims); the rest pass unchanged.  Angles and rotation in float32.
+    ``scaling`` (a dict with ``kind`` and the kind's constants: ``scaled_rotary_frequencies``) stretches the
+    frequencies; ``mult`` is then the factor of the cosines and sines that the kind asks for (1 otherwise).
 
     A mixer whose rotation has constants of its own builds one for itself (``RotaryPositions(
     dims=..., base=...)``) and asks it for ``frequencies(device)``; as a model's ``position``
@@ -73,12 +133,16 @@ class RotaryPositions(Part):
     launches_replayable = True
     rotates = True
 
-    def __init__(self, dims: int, base: float) -> None:
+    def __init__(self, dims: int, base: float, scaling: dict | None = None) -> None:
         if dims < 0 or dims % 2:
             raise ValueError(f"rotary dims {dims}: pairs are turned, the count must be even")
         if base <= 0:
             raise ValueError(f"rotary base {base} must be positive")
         self.dims, self.base = int(dims), float(base)
+        self.scaling = dict(scaling) if scaling else None
+        self._host, self.mult = None, 1.0
+        if self.scaling is not None:
+            self._host, self.mult = scaled_rotary_frequencies(max(self.dims, 2), self.base, self.scaling)
         self._freq: dict = {}
 
     def table(self):
@@ -87,7 +151,8 @@ class RotaryPositions(Part):
     def frequencies(self, device) -> torch.Tensor:
         key = str(device)
         if key not in self._freq:
-            self._freq[key] = rotary_frequencies(max(self.dims, 2), self.base).to(device)
+            host = self._host if self._host is not None else rotary_frequencies(max(self.dims, 2), self.base)
+            self._freq[key] = host.to(device)
         return self._freq[key]
 
 
@@ -184,7 +249,9 @@ class LayerNorm(Part):
 class RMSNorm(Part):
     """``x / sqrt(mean(x^2) + eps) * (weight_offset + weight)`` over the last dimension, in float32
     (``weight_offset`` 1 for scales kept as offsets from one; the sum is formed once, when the
-    weights are bound).
+    weights are bound).  ``out_scale``: a constant that the normalised rows are multiplied by on their way
+    out (a model whose logits are its head's product times a constant gives it to its final norm: the head is
+    linear); it too goes into the weight once, in float32.
 
     ``forward`` normalises rows of the stream for a consumer (a head, a pre-norm block).
     ``add_to`` serves blocks that normalise a sublayer's output instead of its input:
@@ -194,12 +261,13 @@ class RMSNorm(Part):
     graph_safe = True
     launches_replayable = True
 
-    def __init__(self, hidden_size: int, eps: float, weight_offset: float = 0.0) -> None:
+    def __init__(self, hidden_size: int, eps: float, weight_offset: float = 0.0, out_scale: float = 1.0) -> None:
         if eps <= 0:
             raise ValueError("the norm's eps must be positive")
         self.hidden_size = hidden_size
         self.eps = float(eps)
         self.weight_offset = float(weight_offset)
+        self.out_scale = float(out_scale)
         self.weight = None
 
     def param_specs(self):
@@ -209,6 +277,8 @@ class RMSNorm(Part):
         super().bind(tensors)
         if self.weight_offset:
             self.weight = self.weight + self.weight_offset
+        if self.out_scale != 1.0:
+            self.weight = self.weight * self.out_scale
 
     def forward(self, ctx, x, rows=None, n_rows=None, name="normed", defer: bool = False):
         n = x.shape[0] if rows is None else int(n_rows)
@@ -527,6 +597,28 @@ class PreNormBlock(Part):
         if getattr(norm, "can_defer", False) and getattr(consumer, "takes_norm_input", False):
             return norm.forward(ctx, x, defer=True)
         return norm.forward(ctx, x)
+
+
+@register_part("block", "parallel_sublayers")
+class ParallelSublayersBlock(Part):
+    """One norm, both sublayers on its output: with ``h = norm(x)``, ``x += mixer(h) + feed_forward(h)`` (a layer
+    may have no feed-forward).  Both sublayers end in a product that adds into the float32 stream, so the layer
+    is the norm's kernel and the sublayers' own; nothing reads the stream between the two additions."""
+
+    graph_safe = True
+    launches_replayable = True
+
+    def __init__(self, feed_forward: bool = True) -> None:
+        self.has_feed_forward = bool(feed_forward)
+        self.uses = {"norm_input": "norm", "mixer": "mixer"}
+        if feed_forward:
+            self.uses["feed_forward"] = "feed_forward"
+
+    def forward(self, ctx, run, layer, x) -> None:
+        h = layer.norm_input.forward(ctx, x)
+        layer.mixer.forward(ctx, run, h, x)
+        if self.has_feed_forward:
+            layer.feed_forward.forward(ctx, h, x)
 
 
 @register_part("block", "normed_sublayers")

@@ -45,7 +45,15 @@ def random_tensors(
     out: dict[str, torch.Tensor] = {}
     for p in params:
         if p.spec.kind == "int_table":
-            raise ValueError(f"{p.file_name}: no random rule for integer tables")
+            # rows of distinct entries below ``ParamSpec.below``: the first columns of a random order of them
+            rows, cols = p.spec.shape
+            if p.spec.below < cols or p.pieces is not None:
+                raise ValueError(f"{p.file_name}: an integer table's random rows need {cols} distinct entries below "
+                                 f"ParamSpec.below={p.spec.below}, in one piece")
+            g = _generator_for(seed, p.file_name)
+            order = torch.rand((rows, p.spec.below), generator=g).argsort(dim=1)
+            out[p.file_name] = order[:, :cols].to(torch.int32).contiguous()
+            continue
         for name, shape in p.sources():  # a tensor the file holds in pieces: each piece by its own name
             if any(int(e) < 0 for e in shape):
                 raise ValueError(f"{name}: the shape {list(shape)} leaves an extent to the file; random weights "
