@@ -391,10 +391,15 @@ class ModelRunner:
     def _graph_decode_plan(self, b: int):
         """How the decode attention splits keys over blocks in a graph: fixed for the bucket,
         whatever the context lengths of a replay are (splits beyond a request's keys are empty)."""
+        plans = self._graph_decode_plans(b)
+        return max(plans.values()) if plans else None
+
+    def _graph_decode_plans(self, b: int) -> dict:
+        """The same per part (by ``id``): a model whose layers attend in different ways (over all keys, over a
+        window, over latents) cuts each kind's keys as that kind wants them."""
         span = self.max_model_len // 2  # a request's context is anywhere below the limit
-        plans = [part.decode_plan_for(b, span, self.dtype) for l in self.model.layers for part in l.parts.values()
-                 if hasattr(part, "decode_plan_for")]
-        return max(plans) if plans else None
+        return {id(part): part.decode_plan_for(b, span, self.dtype) for l in self.model.layers for part in l.parts.values()
+                if hasattr(part, "decode_plan_for")}
 
     def _stage_decode(self, hb: HostBatch, b: int) -> None:
         """The arrays of a decode-only step of ``b`` rows (``len(hb.slots)`` real, the rest
@@ -433,12 +438,13 @@ class ModelRunner:
         """Capture the decode step of bucket ``b`` on the given (padded) batch."""
         caps = (b, b, b, b, 0, 0)
         ws = Workspace(self.device)  # buffers of its own: their addresses must never change
-        plan = self._graph_decode_plan(b)
+        plan, plans = self._graph_decode_plan(b), self._graph_decode_plans(b)
 
         def context():
             ctx = self._upload(padded, caps)
             ctx.workspace = ws
             ctx.extras["decode_plan"] = plan
+            ctx.extras["decode_plans"] = plans
             if sample_into is not None:
                 ctx.extras["sample_into"] = sample_into
             return ctx

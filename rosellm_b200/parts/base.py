@@ -148,6 +148,16 @@ class Part:
         return ()
 
 
+def step_decode_plan(part: Part, ctx) -> tuple:
+    """How ``part`` cuts the keys of decoded requests in this step: what the engine fixed for a captured step
+    (``ctx.extras["decode_plans"]``: a plan per part, by ``id``; or one plan for all, ``"decode_plan"``), else the
+    part's own ``decode_plan_for`` the step's sizes."""
+    plans = ctx.extras.get("decode_plans")
+    if plans is not None and id(part) in plans:
+        return plans[id(part)]
+    return ctx.extras.get("decode_plan") or part.decode_plan_for(ctx.n_decode, ctx.max_kv_len, ctx.act_dtype)
+
+
 def build_part(category: str, spec: Any, **extra: Any) -> Part:
     cls = part_class(category, spec.kind)
     return cls(**spec.params, **extra)

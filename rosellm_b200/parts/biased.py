@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from .base import KVCacheSpec, ParamSpec, Part, register_part
+from .base import KVCacheSpec, ParamSpec, Part, register_part, step_decode_plan
 from .recurrent import pack_rows
 
 
@@ -76,7 +76,7 @@ class BiasedAttention(Part):
         return max(1, min(8 * K.sm_count() // blocks, tiles // 2, 32)), False
 
     def launch_key(self, ctx) -> tuple:
-        return (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len),) if ctx.n_decode else ()
+        return (step_decode_plan(self, ctx),) if ctx.n_decode else ()
 
     def param_specs(self):
         hid = self.hidden_size
@@ -137,7 +137,7 @@ class BiasedAttention(Part):
         if self._shape is None or self._shape[0] != mma:
             self._shape = (mma, K.bias_attention_shape(self.num_heads // self.num_kv_heads, mma)[1])
         wide = self._shape[1] > 16  # the tokens a block takes must divide the tiles the step is cut into
-        splits = (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len))[0]
+        splits = step_decode_plan(self, ctx)[0]
         part_o = part_ml = None
         if splits > 1:
             rows = ctx.n_decode * self.num_heads * splits

@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from .base import KVCacheSpec, ParamSpec, Part, register_part
+from .base import KVCacheSpec, ParamSpec, Part, register_part, step_decode_plan
 from .recurrent import pack_rows
 from .standard import RotaryPositions
 
@@ -109,7 +109,7 @@ class LatentAttention(Part):
         return self.decode_plan_for(ctx.n_decode, ctx.max_kv_len, ctx.act_dtype)
 
     def launch_key(self, ctx) -> tuple:
-        return (ctx.extras.get("decode_plan") or self.decode_plan(ctx) if ctx.n_decode else None,)
+        return (step_decode_plan(self, ctx) if ctx.n_decode else None,)
 
     def forward(self, ctx, run, h, x, add: bool = True) -> None:
         n, H, W, rank = ctx.n_tokens, self.num_heads, self.row_width, self.kv_rank
@@ -146,7 +146,7 @@ class LatentAttention(Part):
                         rot_mult=self.rotary.mult)
         o_lat = ws.get("latent_o", (n, H * rank), act)
         by_request = ctx.n_decode > 0 and K.latent_decode_fits(H, rank, W)
-        splits = (ctx.extras.get("decode_plan") or self.decode_plan(ctx))[0] if by_request else 1
+        splits = step_decode_plan(self, ctx)[0] if by_request else 1
         part_o = part_ml = None
         if splits > 1:
             parts = ctx.n_decode * H * splits

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from .base import KVCacheSpec, ParamSpec, register_part
+from .base import KVCacheSpec, ParamSpec, register_part, step_decode_plan
 from .biased import BiasedAttention
 from .recurrent import pack_rows
 from .standard import RotaryPositions
@@ -147,7 +147,7 @@ class WindowAttention(BiasedAttention):
         if self._shape is None or self._shape[0] != mma:
             self._shape = (mma, K.bias_attention_shape(self.num_heads // self.num_kv_heads, mma)[1])
         wide = self._shape[1] > 16  # the tokens a block takes must divide the tiles the step is cut into
-        splits = (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len))[0]
+        splits = step_decode_plan(self, ctx)[0]
         part_o = part_ml = None
         if splits > 1:
             rows = ctx.n_decode * self.num_heads * splits

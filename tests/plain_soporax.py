@@ -162,8 +162,11 @@ def latent_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> t
     keys; an element-wise gate on the merged heads."""
     T, h = h.shape[0], _round(h)
     H, dn, dr, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    cq = _round(unit(h @ w[p + "dq"].T, eps) * w[p + "dq.norm"])
-    q = (cq @ w[p + "uq"].T).view(T, H, dn + dr)
+    if m.get("q_rank") is None:  # a model may leave the queries' latent out
+        q = (h @ w[p + "q"].T).view(T, H, dn + dr)
+    else:
+        cq = _round(unit(h @ w[p + "dq"].T, eps) * w[p + "dq.norm"])
+        q = (cq @ w[p + "uq"].T).view(T, H, dn + dr)
     dkv = h @ w[p + "dkv"].T
     c = _round(unit(dkv[:, :rank], eps) * w[p + "dkv.norm"])
     k_rot = dkv[:, rank:]
