@@ -62,6 +62,11 @@ def parse_args():
                    help="instead of the default workload: prefill and decode of the Fikevik design (attention over a window "
                         "beside a matrix memory, linear attention with decaying keys, the norm after each gated sum) beside "
                         "Porovik, the nearest shipped design, at equal width, depth and vocabulary, random weights")
+    p.add_argument("--compare-soporax", action="store_true",
+                   help="instead of the default workload: prefill and decode of the Soporax design (layers whose sublayers "
+                        "share one norm; attention over a window with a sink, rotary attention with a gate per head, latent "
+                        "attention with a query latent; experts named by a table; a stretch of layers run twice) beside "
+                        "Lebedra, the nearest shipped design, at equal width, runs of layers and vocabulary, random weights")
     p.add_argument("--compare-lebedra", action="store_true",
                    help="instead of the default workload: prefill and decode of the Lebedra design (latent attention, "
                         "mixture of experts) beside GPT-2 of equal width, depth and vocabulary, at layer sizes of "
@@ -807,6 +812,74 @@ def compare_fikevik(args):
     return 0
 
 
+# Layer sizes for --compare-soporax: width; the latent attention's heads, plain / turned / value size a head, its
+# key/value latent and query latent; heads, key/value heads and sizes of the two grouped attentions and the window;
+# the dense inner size; experts, experts a token, expert inner size.
+SOPORAX_SIZES = {
+    "1024": dict(width=1024, l_heads=16, l_dim=64, l_rot=32, l_vdim=64, kv_rank=256, q_rank=384, heads=16, kv_heads=4,
+                 dim=64, vdim=64, window=256, ff=4096, experts=16, top=2, expert_ff=1024),
+    "2048": dict(width=2048, l_heads=16, l_dim=128, l_rot=64, l_vdim=128, kv_rank=512, q_rank=768, heads=16, kv_heads=4,
+                 dim=128, vdim=128, window=256, ff=8192, experts=32, top=4, expert_ff=1408),
+}
+
+
+def soporax_config(z: dict, vocab: int, positions: int):
+    """Four layers (latent attention with the dense feed-forward; attention over a window, rotary attention and
+    latent attention with experts); the two in the middle run twice: six runs of layers a step."""
+    from rosellm_b200.config.soporax import SoporaxConfig
+
+    lat = {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["l_rot"], "vdim": z["l_vdim"], "kv_rank": z["kv_rank"],
+           "q_rank": z["q_rank"], "scale": (z["l_dim"] + z["l_rot"]) ** -0.5,
+           "rot": {"dims": z["l_rot"], "base": 250000.0, "scaling": {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}}}
+    grouped = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5}
+    win = dict(grouped, mask={"size": z["window"]})
+    rot = dict(grouped, rot={"dims": z["dim"], "base": 50000.0,
+                             "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}})
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    return SoporaxConfig.from_dict({
+        "architecture": "Soporax", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-5},
+        "logit_scale": 0.5, "loop": {"start": 1, "stop": 3, "times": 2},
+        "layers": [{"type": "latent_attention", "mixer": lat, "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}},
+                   {"type": "attention", "mixer": win, "mlp": moe},
+                   {"type": "attention_2", "mixer": rot, "mlp": moe},
+                   {"type": "latent_attention", "mixer": lat, "mlp": moe}]})
+
+
+def compare_soporax(args):
+    """Prefill (2 x 1024 tokens) and decode (batch 8 and 64, 512 cached tokens) of Soporax and of Lebedra (the
+    nearest shipped design: latent attention, a dense feed-forward in the first layer and experts in the others) at
+    equal width, runs of layers (six) and vocabulary: device time by CUDA events, as the default workload."""
+    runs, vocab, positions = 6, 32000, 1024
+    clocks = Clocks()
+    clocks.start()
+    out = {"metric": "prefill and decode of Soporax beside Lebedra at equal width", "unit": "tokens/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": args.warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+           "data": "synthetic (random token ids, random weights)", "layer_runs": runs, "vocab": vocab, "sizes": {}}
+    for name, z in SOPORAX_SIZES.items():
+        row = {}
+        for label, cfg in (("soporax", soporax_config(z, vocab, positions)),
+                           ("lebedra", lebedra_config(LEBEDRA_SIZES[name], runs, vocab, positions))):
+            h = Harness(cfg, args.dtype, 64, graphs=not args.no_graphs)
+            try:
+                pms = h.prefill()
+                rec = {"prefill_2x1024_ms": round(pms, 4), "prefill_tok_s": round(2048 / (pms * 1e-3), 1),
+                       "weight_mb": round(h.runner.model.weight_bytes() / 1e6, 1)}
+                for b in (8, 64):
+                    ms, launches, gms, _ = h.device_decode(b, args.context, max(16, args.steps // 2), max(4, args.warmup // 2))
+                    rec[f"decode_b{b}_ms"] = round(ms, 4)
+                    rec[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    rec[f"decode_b{b}_launches"] = launches
+                    if gms is not None:
+                        rec[f"decode_b{b}_graph_ms"] = round(gms, 4)
+                row[label] = rec
+            finally:
+                h.close()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     args = parse_args()
     if args.gpus != 1:
@@ -818,6 +891,8 @@ def main():
         return compare_porovik(args)
     if args.compare_fikevik:
         return compare_fikevik(args)
+    if args.compare_soporax:
+        return compare_soporax(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -160,6 +160,77 @@ __global__ __launch_bounds__(256) void moe_table_select_kernel(const int* __rest
   atomicAdd(&counts[e], 1);
 }
 
+// The same routing with its layout, in one block (fused: choice, counts, offsets, tile list and places, which a
+// step of few tokens would otherwise spend three launches on): the counts live in shared memory, the global
+// counters are not touched.  At most MOE_ROUTE_MAX_PAIRS pairs.
+constexpr int MOE_ROUTE_MAX_PAIRS = 8192, MOE_ROUTE_MAX_EXPERTS = 2048;
+
+__global__ __launch_bounds__(1024) void moe_table_route_kernel(const int* __restrict__ token_ids,
+                                                               const int* __restrict__ table, int vocab, int n_tokens,
+                                                               int n_experts, int top, float weight, int* __restrict__ ids,
+                                                               float* __restrict__ weights, int* __restrict__ offsets,
+                                                               int* __restrict__ tiles, int* __restrict__ meta,
+                                                               int* __restrict__ row_token, int* __restrict__ place_of,
+                                                               const int* __restrict__ feedback, int n_feedback,
+                                                               int* __restrict__ status) {
+  __shared__ int count_s[MOE_ROUTE_MAX_EXPERTS], off_s[MOE_ROUTE_MAX_EXPERTS + 1], tile_s[MOE_ROUTE_MAX_EXPERTS + 1];
+  pdl_begin();
+  const int n_pairs = n_tokens * top;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count_s[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int t = i / top, j = i - t * top;
+    int id = token_ids[t];
+    if (id < 0 && feedback != nullptr && -id - 1 < n_feedback) id = feedback[-id - 1];
+    int e = 0;
+    if (id < 0 || id >= vocab) {
+      atomicOr(status, RL_STATUS_BAD_TOKEN);
+    } else {
+      e = table[(size_t)id * top + j];
+      if (e < 0 || e >= n_experts) {
+        atomicOr(status, RL_STATUS_BAD_TOKEN);
+        e = 0;
+      }
+    }
+    ids[i] = e;
+    weights[i] = weight;
+    atomicAdd(&count_s[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tile = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      off_s[e] = at;
+      tile_s[e] = tile;
+      at += count_s[e];
+      tile += (count_s[e] + MOE_TILE_ROWS - 1) / MOE_TILE_ROWS;
+    }
+    off_s[n_experts] = at;
+    tile_s[n_experts] = tile;
+    meta[0] = tile;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    const int c = off_s[e + 1] - off_s[e];
+    for (int k = 0; k * MOE_TILE_ROWS < c; ++k) {
+      int* tl = tiles + 3 * (size_t)(tile_s[e] + k);
+      tl[0] = e;
+      tl[1] = off_s[e] + k * MOE_TILE_ROWS;
+      tl[2] = min(MOE_TILE_ROWS, c - k * MOE_TILE_ROWS);
+    }
+    offsets[e] = off_s[e];
+    count_s[e] = 0;  // from here on: the places handed out
+  }
+  if (threadIdx.x == 0) offsets[n_experts] = off_s[n_experts];
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];  // this thread's own write
+    const int place = off_s[e] + atomicAdd(&count_s[e], 1);
+    row_token[place] = i / top;
+    place_of[i] = place;
+  }
+}
+
 // One block.  offsets[e]: first place of expert e; tiles[k] = (expert, first place, rows);
 // meta[0]: number of tiles.  Leaves counts and fill zero (the scatter that follows counts the
 // places it hands out in fill).
@@ -456,6 +527,25 @@ RL_EXPORT int rl_moe_table_select(const int* token_ids, const int* table, int vo
   if (n_experts <= 0 || n_experts > 2048 || top <= 0 || top > n_experts || vocab <= 0 || status == nullptr) return -2;
   rl::launch_pdl(rl::moe_table_select_kernel, (n_tokens * top + 255) / 256, 256, 0, stream, token_ids, table, vocab,
                  n_tokens, n_experts, top, weight, ids, weights, counts, feedback, n_feedback, status);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// Routing by a table and the layout in one launch: what rl_moe_table_select and rl_moe_plan leave, for at most
+// 8192 pairs (-3 beyond).  No counters in global memory are used.
+RL_EXPORT int rl_moe_table_route(const int* token_ids, const int* table, int vocab, int n_tokens, int n_experts, int top,
+                                 float weight, int* ids, float* weights, int* offsets, int* tiles, int* meta,
+                                 int* row_token, int* place_of, const int* feedback, int n_feedback, int* status,
+                                 cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (n_experts <= 0 || n_experts > rl::MOE_ROUTE_MAX_EXPERTS || top <= 0 || top > n_experts || vocab <= 0 ||
+      status == nullptr)
+    return -2;
+  if ((long)n_tokens * top > rl::MOE_ROUTE_MAX_PAIRS) return -3;
+  const int pairs = n_tokens * top;
+  const int threads = pairs >= 1024 ? 1024 : ((pairs + 31) / 32) * 32;
+  rl::launch_pdl(rl::moe_table_route_kernel, 1, threads, 0, stream, token_ids, table, vocab, n_tokens, n_experts, top,
+                 weight, ids, weights, offsets, tiles, meta, row_token, place_of, feedback, n_feedback, status);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -239,9 +239,10 @@ class Model:
             part.keep_embedding(ctx, x)
         order = self.spec.run_order
         for i, run in enumerate(order):
-            for k, (part, args) in enumerate(self._stream_before.get(i, ())):
-                part.forward(ctx, x, first=(i == 0 and k == 0), **args)
             layer = self.layers[run.layer]
+            before = self._stream_before.get(i, ())
+            for k, (part, args) in enumerate(before):  # the last one may hand the layer its first norm
+                part.forward(ctx, x, first=(i == 0 and k == 0), layer=layer if k == len(before) - 1 else None, **args)
             # a block may finish with work of the layer that runs next (its first norm, say): it finds that layer here
             ctx.extras["next_layer"] = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
             layer.block.forward(ctx, run, layer, x)

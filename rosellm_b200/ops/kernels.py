@@ -160,7 +160,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_latent_kv_write.argtypes = [I, P, L, P, F, P, I, P, P, I, P, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_latent_q_rope.argtypes = [I, P, L, I, I, P, L, I, I, I, I, P, P, I, I, F, P]
         lib.rl_latent_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, P, I, I, I, I, F, P, I, P, I, I, I, P, P, I, P, P]
-        lib.rl_head_linear.argtypes = [I, P, L, L, P, L, L, L, P, L, L, I, I, I, I, P]
+        lib.rl_head_linear.argtypes = [I, P, L, L, P, L, L, L, P, L, L, I, I, I, I, P, L, L, P]
         lib.rl_gated_act.argtypes = [I, P, L, I, P, L, I, I, I, F, F, P]
         lib.rl_token_gate.argtypes = [I, P, L, P, P, L, I, I, P, L, I, I, I, P, I, P, P]
         lib.rl_moe_select.argtypes = [P, L, P, I, I, I, I, I, I, P, P, P, P]
@@ -178,7 +178,9 @@ def _lib() -> ctypes.CDLL:
         lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
         lib.rl_stream_inject.argtypes = [P, L, P, P, L, P, L, I, I, P]
         lib.rl_gate_mul.argtypes = [I, P, L, P, L, I, I, P]
+        lib.rl_stream_inject_norm.argtypes = [I, P, L, P, P, L, P, L, P, F, P, L, I, I, P]
         lib.rl_moe_table_select.argtypes = [P, P, I, I, I, I, F, P, P, P, P, I, P, P]
+        lib.rl_moe_table_route.argtypes = [P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P]
         lib.rl_gated_join_norm.argtypes = [P, L, F, P, L, F, P, L, P, P, P, L, P, L, I, I, F, F, P]
         lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
@@ -186,7 +188,7 @@ def _lib() -> ctypes.CDLL:
                      "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts", "rl_embed_pair",
                      "rl_rmsnorm_add_norm", "rl_recurrence", "rl_recurrence_record", "rl_bias_attention_shape", "rl_bias_attention",
                      "rl_bias_kv_store", "rl_qkv_norm_rotate", "rl_gated_join_norm", "rl_stream_inject", "rl_gate_mul",
-                     "rl_moe_table_select"):
+                     "rl_moe_table_select", "rl_stream_inject_norm", "rl_moe_table_route"):
             getattr(lib, name).restype = I
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
@@ -1078,17 +1080,21 @@ def latent_attention(q, pool, block_table, q_start, kv_len, slots, out, *, sink,
         _launches += (1 if n_tiles else 0) + (1 if n_splits > 1 else 0)
 
 
-def head_linear(inp, w, out, *, n_tokens: int, n_heads: int, k: int, n: int, in_strides, w_strides, out_strides) -> None:
+def head_linear(inp, w, out, *, n_tokens: int, n_heads: int, k: int, n: int, in_strides, w_strides, out_strides,
+                gate=None, gate_strides=(0, 0)) -> None:
     """out[t, h, :n] = inp[t, h, :k] @ W_h for every head: element (t, h, i) of ``inp`` at
     ``t*in_strides[0] + h*in_strides[1] + i``, element (h, i, j) of ``w`` at ``h*w_strides[0] +
     i*w_strides[1] + j*w_strides[2]``, element (t, h, j) of ``out`` at ``t*out_strides[0] +
-    h*out_strides[1] + j`` (strides in elements; the tensors give base addresses and dtype)."""
+    h*out_strides[1] + j`` (strides in elements; the tensors give base addresses and dtype).  ``gate``: float32
+    logits, element (t, h, j) at ``t*gate_strides[0] + h*gate_strides[1] + j``: the result times their sigmoid."""
     _need(inp, "inp", contiguous=False)
     _need(w, "w", inp.dtype)
     _need(out, "out", inp.dtype, contiguous=False)
+    if gate is not None:
+        _need(gate, "gate", torch.float32, contiguous=False)
     rc = _lib().rl_head_linear(_code(inp), _ptr(inp), in_strides[0], in_strides[1], _ptr(w), w_strides[0], w_strides[1],
                                w_strides[2], _ptr(out), out_strides[0], out_strides[1], n_tokens, n_heads, k, n,
-                               _stream())
+                               _ptr(gate), gate_strides[0], gate_strides[1], _stream())
     _ok(rc, "head_linear")
 
 
@@ -1117,9 +1123,10 @@ def gate_mul(o, g) -> None:
     _ok(_lib().rl_gate_mul(_code(o), _ptr(o), o.stride(0), _ptr(g), g.stride(0), o.shape[0], o.shape[1], _stream()), "gate_mul")
 
 
-def stream_inject(x, vec=None, again=None, keep=None) -> None:
+def stream_inject(x, vec=None, again=None, keep=None, norm=None) -> None:
     """``keep <- x`` (where given), then ``x <- x + vec + again``: ``x``, ``again``, ``keep`` float32 [rows, width],
-    ``vec`` float32 [width] added to every row; any of the three may be ``None``."""
+    ``vec`` float32 [width] added to every row; any of the three may be ``None``.  ``norm``: ``(gamma, eps, out)``:
+    the same launch leaves ``out = x / sqrt(mean(x^2) + eps) * gamma`` of the new rows (float32 or bfloat16)."""
     _need(x, "x", torch.float32, contiguous=False)
     n, width = x.shape
     if vec is not None:
@@ -1133,6 +1140,17 @@ def stream_inject(x, vec=None, again=None, keep=None) -> None:
                 raise KernelError(f"stream_inject: {name} has another shape")
     if x.stride(1) != 1 or (again is not None and keep is not None and again.data_ptr() == keep.data_ptr()):
         raise KernelError("stream_inject: rows must be contiguous, and the rows kept are not the rows added")
+    if norm is not None:
+        gamma, eps, out = norm
+        _need(gamma, "gamma", torch.float32)
+        _need(out, "out", contiguous=False)
+        if gamma.numel() != width or tuple(out.shape) != (n, width) or out.stride(1) != 1:
+            raise KernelError("stream_inject: the norm's weight or output has another shape")
+        _ok(_lib().rl_stream_inject_norm(_code(out), _ptr(x), x.stride(0), _ptr(vec), _ptr(again),
+                                         0 if again is None else again.stride(0), _ptr(keep),
+                                         0 if keep is None else keep.stride(0), _ptr(gamma), float(eps), _ptr(out),
+                                         out.stride(0), n, width, _stream()), "stream_inject (with the norm)")
+        return
     _ok(_lib().rl_stream_inject(_ptr(x), x.stride(0), _ptr(vec), _ptr(again), 0 if again is None else again.stride(0),
                                 _ptr(keep), 0 if keep is None else keep.stride(0), n, width, _stream()), "stream_inject")
 
@@ -1193,6 +1211,33 @@ def moe_table_select(token_ids, table, *, n_experts: int, weight: float, ids, we
     if rc == -2:
         raise KernelError(f"moe_table_select: {n_experts} experts, {top} a token not taken")
     _ok(rc, "moe_table_select")
+
+
+MOE_TABLE_ROUTE_MAX_PAIRS = 8192  # csrc/moe.cu: MOE_ROUTE_MAX_PAIRS
+
+
+def moe_table_route(token_ids, table, *, n_experts: int, weight: float, ids, weights, offsets, tiles, meta, row_token,
+                    place_of, feedback=None) -> None:
+    """``moe_table_select`` and ``moe_plan`` in one launch, for at most ``MOE_TABLE_ROUTE_MAX_PAIRS`` (token, choice)
+    pairs: the same ``ids``, ``weights``, ``offsets``, ``tiles``, ``meta``, ``row_token`` and ``place_of``."""
+    _need(token_ids, "token_ids", torch.int32)
+    _need(table, "table", torch.int32)
+    _need(weights, "weights", torch.float32)
+    for t, name in ((ids, "ids"), (offsets, "offsets"), (tiles, "tiles"), (meta, "meta"), (row_token, "row_token"),
+                    (place_of, "place_of")):
+        _need(t, name, torch.int32)
+    vocab, top = table.shape
+    n = token_ids.numel()
+    if min(ids.numel(), weights.numel(), row_token.numel(), place_of.numel()) < n * top or offsets.numel() < n_experts + 1 \
+            or tiles.numel() < 3 * moe_max_tiles(n * top, n_experts):
+        raise KernelError("moe_table_route: the outputs are too small")
+    rc = _lib().rl_moe_table_route(_ptr(token_ids), _ptr(table), vocab, n, n_experts, top, float(weight), _ptr(ids),
+                                   _ptr(weights), _ptr(offsets), _ptr(tiles), _ptr(meta), _ptr(row_token), _ptr(place_of),
+                                   _ptr(feedback), 0 if feedback is None else feedback.numel(),
+                                   _ptr(status_word(table.device)), _stream())
+    if rc in (-2, -3):
+        raise KernelError(f"moe_table_route: {n_experts} experts, {top} a token, {n} tokens not taken")
+    _ok(rc, "moe_table_route")
 
 
 def moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, *, n_tokens: int, n_experts: int, top: int,

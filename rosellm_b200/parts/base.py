@@ -24,10 +24,13 @@ Categories and the signature of ``forward``:
 ``block``          ``forward(ctx, run, layer, x)``: arranges norms, mixer and
                    feed-forward of one layer around the residual stream.
 ``head``           ``forward(ctx, h) -> logits`` ``[rows, vocab]`` float32.
-``stream_input``   ``forward(ctx, x, first=False, **args)``: adds something to the stream between two runs of
-                   layers (``ModelSpec.stream_inputs`` says where and with which ``args``; ``first``: the
-                   stream is the embedding's output as it stands); ``keep_embedding(ctx, x)`` is called
-                   right after the embedding for a part none of whose inputs comes first.
+``stream_input``   ``forward(ctx, x, first=False, layer=None, **args)``: adds something to the stream between
+                   two runs of layers (``ModelSpec.stream_inputs`` says where and with which ``args``;
+                   ``first``: the stream is the embedding's output as it stands; ``layer``: the layer that
+                   runs next, given to the last input ahead of it, which may leave that layer's first norm
+                   in ``ctx.extras["normed_ahead"]`` if the layer's block says it takes it);
+                   ``keep_embedding(ctx, x)`` is called right after the embedding for a part none of whose
+                   inputs comes first.
 """
 from __future__ import annotations
 

@@ -81,6 +81,7 @@ class MixtureOfExperts(Part):
 
     graph_safe = True
     launches_replayable = True
+    _made = 0
 
     def __init__(self, hidden_size: int, inner_size: int, num_experts: int, top: int, group_count: int = 1,
                  group_keep: int = 1, gate: str = "silu", alpha: float = 1.0, limit: float = 0.0,
@@ -91,7 +92,11 @@ class MixtureOfExperts(Part):
         if routing == "table" and (vocab_size <= 0 or correction or group_count != 1):
             raise ValueError("mixture of experts: a routing table needs the vocabulary's size and takes no "
                              "correction and no groups")
+        if routing == "table" and weight_input:
+            raise ValueError("mixture of experts: a routing table weights the experts' outputs")
         self.routing, self.vocab_size = routing, int(vocab_size)
+        MixtureOfExperts._made += 1
+        self._tag = MixtureOfExperts._made  # names this part's own routing buffers in a step's workspace
         if score not in K.MOE_SCORES:
             raise ValueError(f"mixture of experts: score {score!r}; one of {sorted(K.MOE_SCORES)}")
         self.score, self.weight_input = K.MOE_SCORES[score], bool(weight_input)
@@ -123,29 +128,60 @@ class MixtureOfExperts(Part):
             specs.append(ParamSpec("correction", (E,), kind="vector"))
         return specs
 
+    def _table_route(self, ctx):
+        """Routing by the table and its layout.  Both depend on the step's token ids alone, so a part that runs
+        several times in a step (a stretch of layers run in passes) routes once: the buffers are this part's own
+        (named by ``_tag``) and are found again in ``ctx.extras``."""
+        routes = ctx.extras.setdefault("moe_table_routes", {})
+        got = routes.get(id(self))
+        if got is not None:
+            return got
+        n, E, top = ctx.n_tokens, self.num_experts, self.top
+        ws, i32, tag = ctx.workspace, torch.int32, self._tag
+        ids = ws.get(f"moe_ids@{tag}", (n * top,), i32)
+        weights = ws.get(f"moe_weights@{tag}", (n * top,), torch.float32)
+        offsets = ws.get(f"moe_offsets@{tag}", (E + 1,), i32)
+        tiles = ws.get(f"moe_tiles@{tag}", (K.moe_max_tiles(n * top, E) * 3,), i32)
+        meta = ws.get(f"moe_meta@{tag}", (4,), i32)
+        row_token = ws.get(f"moe_row_token@{tag}", (n * top,), i32)
+        place_of = ws.get(f"moe_place_of@{tag}", (n * top,), i32)
+        feedback = ctx.extras.get("token_feedback")
+        if n * top <= K.MOE_TABLE_ROUTE_MAX_PAIRS:
+            K.moe_table_route(ctx.token_ids, self.table, n_experts=E, weight=1.0 / top, ids=ids, weights=weights,
+                              offsets=offsets, tiles=tiles, meta=meta, row_token=row_token, place_of=place_of,
+                              feedback=feedback)
+        else:
+            counts = ws.get_zeroed("moe_counts", (E,), i32)
+            fill = ws.get_zeroed("moe_fill", (E,), i32)
+            K.moe_table_select(ctx.token_ids, self.table, n_experts=E, weight=1.0 / top, ids=ids, weights=weights,
+                               counts=counts, feedback=feedback)
+            K.moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, n_tokens=n, n_experts=E, top=top)
+        got = routes[id(self)] = (weights, tiles, meta, row_token, place_of)
+        return got
+
     def forward(self, ctx, h, x, add: bool = True) -> None:
         n, E, top, f, hid = ctx.n_tokens, self.num_experts, self.top, self.inner_size, self.hidden_size
         ws, i32 = ctx.workspace, torch.int32
-        ids = ws.get("moe_ids", (n * top,), i32)
-        weights = ws.get("moe_weights", (n * top,), torch.float32)
-        counts = ws.get_zeroed("moe_counts", (E,), i32)
-        fill = ws.get_zeroed("moe_fill", (E,), i32)
+        by_place = None
         if self.routing == "table":
-            K.moe_table_select(ctx.token_ids, self.table, n_experts=E, weight=1.0 / top, ids=ids, weights=weights,
-                               counts=counts, feedback=ctx.extras.get("token_feedback"))
+            weights, tiles, meta, row_token, place_of = self._table_route(ctx)
         else:
+            ids = ws.get("moe_ids", (n * top,), i32)
+            weights = ws.get("moe_weights", (n * top,), torch.float32)
+            counts = ws.get_zeroed("moe_counts", (E,), i32)
+            fill = ws.get_zeroed("moe_fill", (E,), i32)
             z = ws.get("moe_logits", (n, E), torch.float32)
             K.linear(h, self.router_weight, None, z)
             K.moe_select(z, self.correction, top=top, group_count=self.group_count, group_keep=self.group_keep, ids=ids,
                          weights=weights, counts=counts, score=self.score)
-        offsets = ws.get("moe_offsets", (E + 1,), i32)
-        tiles = ws.get("moe_tiles", (K.moe_max_tiles(n * top, E) * 3,), i32)
-        meta = ws.get("moe_meta", (4,), i32)
-        row_token = ws.get("moe_row_token", (n * top,), i32)
-        place_of = ws.get("moe_place_of", (n * top,), i32)
-        by_place = ws.get("moe_place_weight", (n * top,), torch.float32) if self.weight_input else None
-        K.moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, n_tokens=n, n_experts=E, top=top,
-                   weights=weights if self.weight_input else None, place_weight=by_place)
+            offsets = ws.get("moe_offsets", (E + 1,), i32)
+            tiles = ws.get("moe_tiles", (K.moe_max_tiles(n * top, E) * 3,), i32)
+            meta = ws.get("moe_meta", (4,), i32)
+            row_token = ws.get("moe_row_token", (n * top,), i32)
+            place_of = ws.get("moe_place_of", (n * top,), i32)
+            by_place = ws.get("moe_place_weight", (n * top,), torch.float32) if self.weight_input else None
+            K.moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, n_tokens=n, n_experts=E, top=top,
+                       weights=weights if self.weight_input else None, place_weight=by_place)
         act = ws.get("moe_inner", (n * top, f), ctx.act_dtype)
         eo = ws.get("moe_expert_out", (n * top, hid), torch.float32)
         K.moe_experts(h, self.gate_up_weight, self.down_weight, tiles, meta, row_token, place_of,

@@ -161,11 +161,12 @@ class LatentAttention(Part):
             o = ws.get_zeroed(f"latent_heads_{self.heads_width}", (n, self.heads_padded), act)
         else:
             o = ws.get("latent_heads", (n, self.heads_padded), act)
+        gate, gate_strides = None, (0, 0)
+        if self.has_gate:  # the merged heads' gate rides on the product that makes them
+            gate, gate_strides = proj[:, off["g"]:off["g"] + self.heads_width], (proj.stride(0), self.value_dim)
         K.head_linear(o_lat, self.uv_weight, o, n_tokens=n, n_heads=H, k=rank, n=self.value_dim,
                       in_strides=(H * rank, rank), w_strides=(self.value_dim * rank, 1, rank),
-                      out_strides=(self.heads_padded, self.value_dim))
-        if self.has_gate:
-            K.gate_mul(o[:, :self.heads_width], proj[:, off["g"]:off["g"] + self.heads_width])
+                      out_strides=(self.heads_padded, self.value_dim), gate=gate, gate_strides=gate_strides)
         K.linear(o, self.o_weight, None, x, residual=add)
 
 

@@ -608,6 +608,10 @@ class ParallelSublayersBlock(Part):
     graph_safe = True
     launches_replayable = True
 
+    # the sub-part whose output ``ctx.extras["normed_ahead"]`` stands for, when whatever wrote the stream last has
+    # normalised its rows in the same launch
+    takes_normed_ahead = "norm_input"
+
     def __init__(self, feed_forward: bool = True) -> None:
         self.has_feed_forward = bool(feed_forward)
         self.uses = {"norm_input": "norm", "mixer": "mixer"}
@@ -615,7 +619,9 @@ class ParallelSublayersBlock(Part):
             self.uses["feed_forward"] = "feed_forward"
 
     def forward(self, ctx, run, layer, x) -> None:
-        h = layer.norm_input.forward(ctx, x)
+        h = ctx.extras.pop("normed_ahead", None)
+        if h is None:
+            h = layer.norm_input.forward(ctx, x)
         layer.mixer.forward(ctx, run, h, x)
         if self.has_feed_forward:
             layer.feed_forward.forward(ctx, h, x)

@@ -10,6 +10,7 @@ import torch
 
 from ..ops import kernels as K
 from .base import ParamSpec, Part, register_part
+from .standard import RMSNorm
 
 
 @register_part("stream_input", "pass_input")
@@ -42,9 +43,18 @@ class PassInput(Part):
         if self.wants_embedding:
             K.stream_inject(x, keep=self._kept(ctx, x))
 
-    def forward(self, ctx, x, first: bool = False, index: int = 0) -> None:
+    def forward(self, ctx, x, first: bool = False, layer=None, index: int = 0) -> None:
         if not 0 <= index < self.passes:
             raise ValueError(f"pass input: pass {index} of {self.passes}")
         keep = self._kept(ctx, x) if first and self.wants_embedding else None
         again = self._kept(ctx, x) if index > 0 and self.readd_embedding else None
-        K.stream_inject(x, vec=self.table[index], again=again, keep=keep)
+        # where the layer that runs next begins with an RMS norm of the stream and takes it ready-made, the same
+        # launch leaves it (fused: no kernel of its own normalises the rows this one has just written)
+        name = getattr(getattr(layer, "block", None), "takes_normed_ahead", None)
+        norm = getattr(layer, name, None) if name else None
+        if isinstance(norm, RMSNorm):
+            out = ctx.workspace.get("normed", tuple(x.shape), ctx.act_dtype)
+            K.stream_inject(x, vec=self.table[index], again=again, keep=keep, norm=(norm.weight, norm.eps, out))
+            ctx.extras["normed_ahead"] = out
+        else:
+            K.stream_inject(x, vec=self.table[index], again=again, keep=keep)
