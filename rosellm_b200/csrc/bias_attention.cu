@@ -417,6 +417,10 @@ static void dispatch_bias_attn_types(int cache_dtype, int out_dtype, const BiasA
 
 }  // namespace rl
 
+// For comparisons: whether prompt tiles on the tensor cores may take the form whose key tiles travel by cp.async
+// (on by default; sizes that cannot be copied in 16-byte pieces never take it).
+RL_EXPORT void rl_bias_attention_async(int on) { rl::BIAS_ATTENTION_ASYNC = on != 0; }
+
 // How the `rows` rows of a prompt tile's block (32: the CUDA-core kernel; 64: the tensor-core kernel) are cut
 // into tokens and heads for `heads_per_group` query heads a key/value head: heads a block (at most `rows`) and
 // tokens a block (a power of two, at most `rows`).

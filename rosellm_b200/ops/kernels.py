@@ -1407,6 +1407,16 @@ def bias_attention_tensor_cores(dtype: torch.dtype, dk: int, dv: int) -> bool:
     return BIAS_ATTENTION_TENSOR_CORES and dtype == torch.bfloat16 and dk <= 128 and dv <= 128
 
 
+def bias_attention_async(on: bool) -> None:
+    """For comparisons and tests: let the tensor-core prompt tiles take the form whose key and value tiles travel
+    by cp.async through a ring of two stages (the default, where cache rows can be copied in 16-byte pieces), or
+    keep every size on the form that copies them through registers."""
+    lib = _lib()
+    lib.rl_bias_attention_async.argtypes = [c_int]
+    lib.rl_bias_attention_async.restype = None
+    lib.rl_bias_attention_async(int(bool(on)))
+
+
 def bias_attention_shape(heads_per_group: int, tensor_cores: bool = False) -> tuple[int, int]:
     """(heads a block, tokens a block) of ``bias_attention``'s prompt tiles for so many query heads a
     key/value head: of the 32 rows of the CUDA-core kernel's blocks, or the 64 of the tensor-core kernel's."""

@@ -286,6 +286,24 @@ def test_attention_with_a_sink_and_gates(dtype, window, gate):
             assert rel(got, want) < _tol(dtype, mma), (H, G, dk, dv, mma, "single tokens")
 
 
+@pytest.mark.parametrize("window", [None, 1, 100])
+def test_both_forms_of_the_tensor_core_prompt_tiles(window):
+    """Key and value tiles by cp.async through two stages (portions of one to many tiles, contexts that begin
+    inside a tile, tiles that are partly or wholly outside the window) against the form that copies them through
+    registers, and both against the plain result."""
+    for H, G, dk, dv, page in ((8, 2, 64, 64, 16), (4, 1, 48, 24, 8), (16, 4, 128, 128, 16), (3, 3, 16, 120, 32)):
+        got = {}
+        for on in (True, False):
+            K().bias_attention_async(on)
+            try:
+                got[on], want, _ = _attn_case("bfloat16", H, G, dk, dv, [200, 1, 2, 65, 64, 700], [5, 130, 0, 63, 64, 330], page, 0.3,
+                                              window, seed=H, mma=True, gate="head")
+            finally:
+                K().bias_attention_async(True)
+            assert rel(got[on], want) < _tol("bfloat16", True), (H, G, dk, dv, on)
+        assert rel(got[True], got[False]) < 1e-2
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("sink", [None, 0.0, -30.0, 4.0, 25.0])
 def test_sinks_of_every_size(dtype, sink):
