@@ -66,10 +66,12 @@ def test_output_gate_on_merged_heads(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("experts,top,n", [(5, 2, 150), (1, 1, 9), (9, 1, 3), (3, 3, 70), (16, 4, 1), (8, 2, 600)])
+@pytest.mark.parametrize("experts,top,n", [(5, 2, 150), (1, 1, 9), (9, 1, 3), (3, 3, 70), (16, 4, 1), (8, 2, 600), (6, 3, 2800)])
 def test_experts_named_by_a_table_of_token_ids(dtype, experts, top, n):
-    """The part itself on a step's tokens: few tokens (every expert's weights streamed once) and many (tiles);
-    all experts a token, one, and a single expert; token ids the engine feeds back from the device."""
+    """The part itself on a step's tokens: few tokens (every expert's weights streamed once) and many (tiles), also
+    more pairs than the one-launch routing takes (three launches then); all experts a token, one, and a single
+    expert; token ids the engine feeds back from the device; a second run of the part in the same step, which
+    finds the step's routing again."""
     from rosellm_b200.engine.context import Workspace
     from rosellm_b200.parts.gated import MixtureOfExperts
 
@@ -101,6 +103,10 @@ def test_experts_named_by_a_table_of_token_ids(dtype, experts, top, n):
         part.forward(ctx, h.to(DEV), x, add=True)
         K().check_status(torch.device(DEV))
         assert rel(x.cpu().double() - x0.double(), want) < (2e-5 if dtype == "float32" else 1.5e-2)
+        before = K().launches()
+        x2 = torch.zeros(n, hid, device=DEV)
+        part.forward(ctx, h.to(DEV), x2, add=False)  # the same step again: no routing launches, the same result
+        assert K().launches() - before == 3 and rel(x2, want) < (2e-5 if dtype == "float32" else 1.5e-2)
 
 
 @pytest.mark.parametrize("H,G,dk,dv,rot", [(6, 2, 20, 12, 12), (4, 4, 64, 32, 0), (7, 1, 9, 5, 8), (2, 1, 136, 130, 136)])
