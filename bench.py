@@ -830,11 +830,11 @@ def soporax_config(z: dict, vocab: int, positions: int):
 
     lat = {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["l_rot"], "vdim": z["l_vdim"], "kv_rank": z["kv_rank"],
            "q_rank": z["q_rank"], "scale": (z["l_dim"] + z["l_rot"]) ** -0.5,
-           "rot": {"dims": z["l_rot"], "base": 250000.0, "scaling": {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}}}
+           "rot": {"dims": z["l_rot"], "base": 10000.0, "scaling": {"factor": 8.0, "original": 256, "fast": 16.0, "slow": 2.0}}}
     grouped = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5}
     win = dict(grouped, mask={"size": z["window"]})
-    rot = dict(grouped, rot={"dims": z["dim"], "base": 50000.0,
-                             "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}})
+    rot = dict(grouped, rot={"dims": z["dim"], "base": 500000.0,
+                             "scaling": {"factor": 8.0, "low": 2.0, "high": 8.0, "original": 256}})
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
     return SoporaxConfig.from_dict({
         "architecture": "Soporax", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-5},

@@ -62,7 +62,7 @@ def model(vocab, width, eps, logit_scale, loop, layers):
 RAW_A = model(131, 64, 1e-5, 1.7, (1, 3, 3), [
     (latent(3, 12, 6, 10, 18, 20, 0.21, 10000.0, (8.0, 32, 16.0, 2.0)), dense(100, 0.7)),
     (windowed(6, 2, 20, 12, 0.3, 7), moe(5, 2, 24)),
-    (rotary(4, 4, 16, 8, 0.25, 12, 500.0, (4.0, 1.0, 4.0, 16)), None),
+    (rotary(4, 4, 16, 8, 0.25, 12, 500.0, (3.0, 1.5, 5.0, 16)), None),
     (windowed(3, 3, 8, 24, 0.4, 40), dense(36, 3.0)),
 ])
 RAW_B = model(300, 96, 1e-6, 1.0, None, [
@@ -78,7 +78,7 @@ RAW_C = model(77, 48, 1e-4, 0.35, (0, 3, 2), [
 ])
 RAW_D = model(2000, 384, 1e-5, 2.5, (2, 3, 4), [
     (rotary(12, 4, 48, 80, 0.14, 32, 300000.0, (8.0, 1.0, 4.0, 96)), dense(640, 7.0)),
-    (latent(6, 64, 32, 96, 200, 136, 0.1, 250000.0, (4.0, 64, 32.0, 1.0)), moe(6, 4, 96)),
+    (latent(6, 64, 32, 96, 200, 136, 0.1, 100000.0, (16.0, 64, 24.0, 1.5)), moe(6, 4, 96)),
     (windowed(2, 1, 136, 130, 0.09, 48), dense(96, 1.0)),
     (latent(4, 24, 16, 24, 72, 48, 0.16, 5000.0, (40.0, 48, 8.0, 2.0)), moe(4, 2, 128)),
 ])
@@ -101,9 +101,9 @@ TINY = {
 }
 # A wide one: the products' tensor-core paths, windows of many key tiles, a latent of 256.
 RAW_WIDE = model(3000, 1024, 1e-5, 0.5, (0, 2, 2), [
-    (latent(16, 64, 32, 64, 256, 384, 0.1, 250000.0, (4.0, 128, 32.0, 1.0)), dense(2048, 7.0)),
+    (latent(16, 64, 32, 64, 256, 384, 0.1, 1.0e6, (16.0, 128, 24.0, 2.0)), dense(2048, 7.0)),
     (windowed(16, 4, 64, 64, 0.125, 300), moe(8, 2, 512)),
-    (rotary(16, 2, 128, 128, 0.09, 64, 50000.0, (4.0, 1.0, 4.0, 256)), dense(1024, 2.0)),
+    (rotary(16, 2, 128, 128, 0.09, 64, 20000.0, (8.0, 2.0, 6.0, 256)), dense(1024, 2.0)),
 ])
 WIDE = dict(raw=RAW_WIDE, seed=71, std=0.03, page_size=16)
 
