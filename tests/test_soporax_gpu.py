@@ -184,6 +184,21 @@ def test_latent_rows_and_queries_with_scaled_cosines(dtype):
     assert rel(rows.view(n, H, rows_w)[..., rank:rank + rot_dim].float(), want) < tol
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", [0, 15, 16, 512, 897])
+def test_latent_attention_with_a_plain_softmax_finds_a_far_key(dtype, key):
+    """The latent mixer of this design has no sink: among 900 cached rows one is scored far above the rest, as the
+    first key, at a page's border and far back, from a prompt portion's query and from a decoded token's (keys cut
+    into parts); the case builder is the one of the latent kernels' own tests."""
+    from test_lebedra_gpu import _attention_case as latent_case
+
+    for new, old, by_request, splits in (([4], [896], False, 1), ([1], [899], True, 4), ([1], [899], True, 1)):
+        got, want = latent_case(dtype, 2, 24, 8, new, old, 16, None, 1.0, by_request, splits, seed=key,
+                                stand_out=(new[0] - 1, key))
+        assert rel(got, want) < (2e-5 if dtype == "float32" else 2e-2)
+        assert (want[-1, 0].abs() > 0.05).any()
+
+
 def _attn_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, window, seed, stand_out=None, splits=1, mma=False,
                sink="random", gate=None):
     """Requests with ``lens_old`` cached tokens bring ``lens_new`` more.  All tokens' cache rows are written by the
