@@ -523,7 +523,20 @@ namespace rl {
 //     divided by the root mean square and no weight), then the first
 //     `rot_dims` entries turned, entry 2i with entry 2i + 1, by the angle position * freq[i];
 //   values: each head's entries divided by their root mean square, no weight (unit_values; else untouched).
-// Angles are formed and evaluated in float32.
+// Angles are formed and evaluated in float32.  With a cache target the keys and values go into their pages on the
+// way (as `bias_kv_store_kernel` would put them) and are not written back.
+// Where the keys and values of a step go when this kernel also writes the cache (fused: the store kernel's work
+// rides on the pass that normalises and rotates; keys and values are then NOT written back in place).
+struct QkvCacheTarget {
+  void* pool;  // [pages, 1, n_kv, page_size, row], or null: no store
+  const int* block_table;
+  long ldt;
+  const int *req_of_token, *slots;
+  int v_at, row, page_size, max_pages;
+  int* status;
+};
+
+template <typename T>
 __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict__ q, long ldq, float* __restrict__ k,
                                                               long ldk, float* __restrict__ v, long ldv,
                                                               const float* __restrict__ q_norm,
@@ -531,13 +544,33 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
                                                               const float* __restrict__ freq,
                                                               const int* __restrict__ positions, int n_tokens,
                                                               int n_heads, int n_kv, int dk, int dv, int rot_dims,
-                                                              int unit_values, int unit_qk, float eps) {
+                                                              int unit_values, int unit_qk, float eps,
+                                                              const QkvCacheTarget c) {
   pdl_begin();
   const int tok = blockIdx.x;
   if (tok >= n_tokens) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-  const float pos = (float)positions[tok];
-  const int units = n_heads + n_kv + (unit_values ? n_kv : 0);
+  const int ipos = positions[tok];
+  const float pos = (float)ipos;
+  const bool store = c.pool != nullptr;
+  const int units = n_heads + n_kv + ((unit_values || store) ? n_kv : 0);
+  // the token's place in the cache: a row of its page a key/value head (null: a padding row, or no page)
+  T* cache_row = nullptr;
+  long head_step = 0;
+  if (store) {
+    const int slot = c.slots[c.req_of_token[tok]];
+    if (slot >= 0) {
+      const int lp = ipos / c.page_size;
+      const int page = (ipos >= 0 && lp < c.max_pages) ? c.block_table[(size_t)slot * c.ldt + lp] : -1;
+      if (page < 0) {
+        if (threadIdx.x == 0 && blockIdx.y == 0)
+          atomicOr(c.status, ipos < 0 || lp >= c.max_pages ? RL_STATUS_BAD_POSITION : RL_STATUS_BAD_PAGE);
+      } else {
+        head_step = (long)c.page_size * c.row;
+        cache_row = reinterpret_cast<T*>(c.pool) + ((size_t)page * n_kv * c.page_size + (ipos - lp * c.page_size)) * c.row;
+      }
+    }
+  }
   // the token's angles are the same for all its heads: their sines and cosines once a block
   __shared__ float2 turn[128];
   for (int i = threadIdx.x; 2 * i < rot_dims; i += blockDim.x) sincosf(pos * freq[i], &turn[i].y, &turn[i].x);
@@ -547,6 +580,8 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
       const bool is_q = u < n_heads;
       float* e = is_q ? q + (size_t)tok * ldq + (size_t)u * dk : k + (size_t)tok * ldk + (size_t)(u - n_heads) * dk;
       const float* w = is_q ? q_norm : k_norm;
+      T* to_cache = (!is_q && cache_row != nullptr) ? cache_row + (size_t)(u - n_heads) * head_step : nullptr;
+      const bool in_place = is_q || !store;
       float r = 1.0f;
       if (w != nullptr || unit_qk) {
         float ss = 0.f;
@@ -566,15 +601,30 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
           a = ra;
           b = rb;
         }
-        e[d0] = a;
-        if (d1 < dk) e[d1] = b;
+        if (in_place) {
+          e[d0] = a;
+          if (d1 < dk) e[d1] = b;
+        }
+        if (to_cache != nullptr) {
+          to_cache[d0] = from_f32<T>(a);
+          if (d1 < dk) to_cache[d1] = from_f32<T>(b);
+        }
       }
     } else {
-      float* e = v + (size_t)tok * ldv + (size_t)(u - n_heads - n_kv) * dv;
-      float ss = 0.f;
-      for (int d = lane; d < dv; d += 32) ss = fmaf(e[d], e[d], ss);
-      const float r = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
-      for (int d = lane; d < dv; d += 32) e[d] *= r;
+      const int g = u - n_heads - n_kv;
+      float* e = v + (size_t)tok * ldv + (size_t)g * dv;
+      float r = 1.0f;
+      if (unit_values) {
+        float ss = 0.f;
+        for (int d = lane; d < dv; d += 32) ss = fmaf(e[d], e[d], ss);
+        r = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+      }
+      if (!store) {
+        for (int d = lane; d < dv; d += 32) e[d] *= r;
+      } else if (cache_row != nullptr) {
+        T* to_cache = cache_row + (size_t)g * head_step + c.v_at;
+        for (int d = lane; d < dv; d += 32) to_cache[d] = from_f32<T>(e[d] * r);
+      }
     }
   }
 }
@@ -585,20 +635,32 @@ __global__ __launch_bounds__(128) void qkv_norm_rotate_kernel(float* __restrict_
 // strides given) normalised and rotated in place; see the kernel.  q_norm / k_norm: float32 [dk] or null (both
 // or neither; unit_qk: without weights, queries and keys are still divided by their root mean square);
 // freq: float32 [rot_dims / 2] (rot_dims even, at most dk; 0: no rotation).
+// pool (or null): the cache [pages, 1, n_kv, page_size, row] of element type cache_dtype: keys and values go to
+// their pages (the value at entry v_at of a row) instead of back in place, as rl_bias_kv_store would put them.
 RL_EXPORT int rl_qkv_norm_rotate(float* q, long ldq, float* k, long ldk, float* v, long ldv, const float* q_norm,
                                  const float* k_norm, const float* freq, const int* positions, int n_tokens, int n_heads,
                                  int n_kv, int dk, int dv, int rot_dims, int unit_values, int unit_qk, float eps,
+                                 int cache_dtype, void* pool, const int* block_table, long ldt, const int* req_of_token,
+                                 const int* slots, int v_at, int row, int page_size, int max_pages, int* status,
                                  cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || dk <= 0 || dv <= 0 || rot_dims < 0 || rot_dims % 2 || rot_dims > dk ||
       rot_dims > 256 || (rot_dims > 0 && freq == nullptr) || (q_norm == nullptr) != (k_norm == nullptr))
     return -2;
-  const int units = n_heads + n_kv + (unit_values ? n_kv : 0);
+  if (pool != nullptr && (block_table == nullptr || req_of_token == nullptr || slots == nullptr || status == nullptr ||
+                          v_at < dk || v_at + dv > row || page_size <= 0))
+    return -2;
+  const int units = n_heads + n_kv + ((unit_values || pool != nullptr) ? n_kv : 0);
   // a warp a (token, head) in a step of few tokens; with many tokens a block takes more of a token's heads
   const int want = (148 * 40 + n_tokens - 1) / n_tokens, most = units < 4 * 1024 ? (units + 3) / 4 : 1024;
   const int rows = want < most ? want : most;
-  rl::launch_pdl(rl::qkv_norm_rotate_kernel, dim3(n_tokens, rows), 128, 0, stream, q, ldq, k, ldk, v, ldv, q_norm, k_norm,
-                 freq, positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, unit_qk, eps);
+  const rl::QkvCacheTarget c{pool, block_table, ldt, req_of_token, slots, v_at, row, page_size, max_pages, status};
+  if (pool != nullptr && cache_dtype == RL_F32)
+    rl::launch_pdl(rl::qkv_norm_rotate_kernel<float>, dim3(n_tokens, rows), 128, 0, stream, q, ldq, k, ldk, v, ldv, q_norm,
+                   k_norm, freq, positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, unit_qk, eps, c);
+  else
+    rl::launch_pdl(rl::qkv_norm_rotate_kernel<__nv_bfloat16>, dim3(n_tokens, rows), 128, 0, stream, q, ldq, k, ldk, v, ldv,
+                   q_norm, k_norm, freq, positions, n_tokens, n_heads, n_kv, dk, dv, rot_dims, unit_values, unit_qk, eps, c);
   RL_CHECK_LAUNCH();
   return 0;
 }

@@ -175,7 +175,8 @@ def _lib() -> ctypes.CDLL:
         lib.rl_bias_attention_shape.argtypes = [I, I, P, P]
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
                                           F, F, I, P, P, I, P, P, I, I, P, P, I, P]
-        lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
+        lib.rl_qkv_norm_rotate.argtypes = [P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, I, I, I, F,
+                                           I, P, P, L, P, P, I, I, I, I, P, P]
         lib.rl_stream_inject.argtypes = [P, L, P, P, L, P, L, I, I, P]
         lib.rl_gate_mul.argtypes = [I, P, L, P, L, I, I, P]
         lib.rl_stream_inject_norm.argtypes = [I, P, L, P, P, L, P, L, P, F, P, L, I, I, P]
@@ -1509,13 +1510,25 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
     _ok(rc, "bias_attention")
 
 
+class QkvCache:
+    """Where ``qkv_norm_rotate`` puts the step's keys and values: the pool ``[pages, 1, kv heads, page, row]`` (the
+    value at entry ``v_at`` of a row), the block table and the step's request and slot arrays."""
+
+    def __init__(self, pool, block_table, req_of_token, slots, v_at: int, max_pos: int) -> None:
+        self.pool, self.block_table, self.req_of_token, self.slots = pool, block_table, req_of_token, slots
+        self.v_at, self.max_pos = int(v_at), int(max_pos)
+
+
 def qkv_norm_rotate(q, k, v, positions, *, n_heads: int, n_kv: int, dk: int, dv: int, eps: float, q_norm=None, k_norm=None,
-                    freq=None, rot_dims: int = 0, unit_values: bool = False, unit_qk: bool = False) -> None:
+                    freq=None, rot_dims: int = 0, unit_values: bool = False, unit_qk: bool = False,
+                    cache: "QkvCache | None" = None) -> None:
     """In place on float32 views (row strides allowed): every head of ``q`` [tokens, heads * dk] and ``k``
     [tokens, kv heads * dk] divided by its root mean square and multiplied by ``q_norm`` / ``k_norm`` (float32
     [dk], both or neither), then its first ``rot_dims`` entries turned in neighbouring pairs by position *
     ``freq[i]``; with ``unit_values`` every head of ``v`` [tokens, kv heads * dv] divided by its root mean square;
-    with ``unit_qk`` (and no weights) every head of q and k divided by its root mean square and left so."""
+    with ``unit_qk`` (and no weights) every head of q and k divided by its root mean square and left so.
+    ``cache`` (a ``QkvCache``): keys and values go into their cache pages as ``bias_kv_store`` would put them (and
+    are not written back in place): no store kernel is needed behind this one."""
     for t, name, width in ((q, "q", n_heads * dk), (k, "k", n_kv * dk), (v, "v", n_kv * dv)):
         _need(t, name, torch.float32, contiguous=False)
         if t.shape[1] != width or t.stride(1) != 1 or t.shape[0] != q.shape[0]:
@@ -1529,9 +1542,20 @@ def qkv_norm_rotate(q, k, v, positions, *, n_heads: int, n_kv: int, dk: int, dv:
         _need(freq, "freq", torch.float32)
         if freq.numel() < rot_dims // 2:
             raise KernelError("qkv_norm_rotate: one frequency a turned pair")
+    cx = (0, None, None, 0, None, None, 0, 0, 0, 0, None)
+    if cache is not None:
+        pool = cache.pool
+        _need(pool, "cache.pool")
+        _need(cache.block_table, "cache.block_table", torch.int32)
+        _, planes, heads, page_size, row = pool.shape
+        if planes != 1 or heads != n_kv or cache.v_at < dk or cache.v_at + dv > row:
+            raise KernelError("qkv_norm_rotate: the cache's rows do not fit the keys and values")
+        cx = (_code(pool), _ptr(pool), _ptr(cache.block_table), cache.block_table.stride(0), _ptr(cache.req_of_token),
+              _ptr(cache.slots), int(cache.v_at), row, page_size,
+              min(cache.block_table.shape[1], -(-cache.max_pos // page_size)), _ptr(status_word(pool.device)))
     rc = _lib().rl_qkv_norm_rotate(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(q_norm), _ptr(k_norm),
                                    _ptr(freq) if rot_dims else None, _ptr(positions), q.shape[0], n_heads, n_kv, dk, dv,
-                                   int(rot_dims), int(bool(unit_values)), int(bool(unit_qk)), float(eps), _stream())
+                                   int(rot_dims), int(bool(unit_values)), int(bool(unit_qk)), float(eps), *cx, _stream())
     if rc == -2:
         raise KernelError("qkv_norm_rotate: sizes not taken (an even number of turned entries, at most the key size; "
                           "both norms or neither)")

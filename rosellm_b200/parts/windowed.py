@@ -128,13 +128,17 @@ class WindowAttention(BiasedAttention):
         v = proj[:, o["v"]:o["v"] + self.v_width]
         gate = proj[:, o["g"]:o["g"] + self.gate_width] if self.has_gate else None
         pool, table = ctx.kv_pool(run.cache_key), ctx.block_table(run.cache_key)
+        stored = False
         if self.qk_norm or self.rot_dims or self.unit_values:
+            # the same pass puts the step's keys and values into their pages (fused: no store kernel behind it)
+            stored = run.writes_cache
+            target = K.QkvCache(pool, table, ctx.req_of_token, ctx.slots, self.v_at, ctx.cache.max_seq_len) if stored else None
             K.qkv_norm_rotate(q, k, v, ctx.positions, n_heads=self.num_heads, n_kv=self.num_kv_heads, dk=self.key_dim,
                               dv=self.value_dim, eps=self.norm_eps, q_norm=self.q_norm, k_norm=self.k_norm,
                               freq=self.rotary.frequencies(ctx.device) if self.rotary is not None else None,
                               rot_dims=self.rot_dims, unit_values=self.unit_values,
-                              unit_qk=self.qk_norm and not self.qk_norm_weights)
-        if run.writes_cache:
+                              unit_qk=self.qk_norm and not self.qk_norm_weights, cache=target)
+        if run.writes_cache and not stored:
             K.bias_kv_store(k, v, pool, table, ctx.positions, ctx.req_of_token, ctx.slots, v_at=self.v_at,
                             max_pos=ctx.cache.max_seq_len)
         if self.out_padded == self.out_width:

@@ -146,6 +146,45 @@ def test_unit_queries_and_keys_and_stretched_rotations(H, G, dk, dv, rot):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,dk,dv,rot,unit_v", [(6, 2, 20, 12, 12, False), (4, 4, 64, 32, 0, True), (7, 1, 9, 5, 8, False),
+                                                  (2, 1, 136, 130, 136, True)])
+def test_keys_and_values_into_their_pages_by_the_pass_that_normalises_them(dtype, H, G, dk, dv, rot, unit_v):
+    """The pass with a cache target against the pass in place followed by the store kernel: the same pages bit for
+    bit, the same queries; requests that start inside a page and cross page borders; a padding row (slot -1) writes
+    nothing."""
+    from rosellm_b200.engine.context import build_host_batch
+    from rosellm_b200.parts.standard import RotaryPositions
+
+    dt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(H + dk)
+    page, v_at = 8, -(-dk // 8) * 8
+    row = -(-(v_at + dv) // 8) * 8
+    hb = build_host_batch([(1, 5, [0] * 20, []), (2, 0, [0] * 3, []), (3, 31, [0], []), (-1, 0, [0], [])])
+    n = len(hb.positions)
+    table = torch.full((4, 8), -1, dtype=torch.int32)
+    table[1:, :] = torch.randperm(24, generator=g).view(3, 8).to(torch.int32)
+    q, k, v = (torch.randn(n, w, generator=g) for w in (H * dk, G * dk, G * dv))
+    freq = RotaryPositions(dims=rot, base=300.0).frequencies(DEV) if rot else None
+    pools, queries = [], []
+    for fused in (False, True):
+        pool = torch.full((24, 1, G, page, row), 7.0, dtype=dt, device=DEV)
+        bq, bk, bv = q.to(DEV).clone(), k.to(DEV).clone(), v.to(DEV).clone()
+        cache = K().QkvCache(pool, table.to(DEV), dev(hb.req_of_token), dev(hb.slots), v_at, 64) if fused else None
+        K().qkv_norm_rotate(bq, bk, bv, dev(hb.positions), n_heads=H, n_kv=G, dk=dk, dv=dv, eps=1e-5, freq=freq, rot_dims=rot,
+                            unit_values=unit_v, unit_qk=True, cache=cache)
+        if fused:
+            assert torch.equal(bk.cpu(), k) and torch.equal(bv.cpu(), v)  # not written back
+        else:
+            K().bias_kv_store(bk, bv, pool, table.to(DEV), dev(hb.positions), dev(hb.req_of_token), dev(hb.slots), v_at=v_at,
+                              max_pos=64)
+        K().check_status(torch.device(DEV))
+        pools.append(pool.float().cpu())
+        queries.append(bq.cpu())
+    assert torch.equal(pools[0], pools[1]) and torch.equal(queries[0], queries[1])
+    assert (pools[1] != 7.0).sum() == (n - 1) * G * (dk + dv)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_latent_rows_and_queries_with_scaled_cosines(dtype):
     """The cache rows and the queries' turned parts with a factor on cosines and sines, frequencies of the ramp."""
     from rosellm_b200.parts.standard import RotaryPositions
